@@ -1,0 +1,431 @@
+"""Benchmark of the SiHC read/write path: fused hyper-connection read + write, forward and backward.
+
+One "step" = one pass of the hot path over one batch of synthetic input:
+    read fwd -> write fwd -> read bwd (dX + dalpha) -> write bwd (ddz + dbeta)
+on a single connection event (the op-level definition of the headline metric,
+"SiHC read/write fwd+bwd HBM GB/s").  Bytes are ALGORITHMIC bytes: per token and
+channel element, read fwd S+1, write fwd 2S+1, read bwd 2S+1, write bwd S+2
+(total 6S+5 elements of the activation dtype).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Under torchrun (N > 1) every rank runs the same per-GPU workload on its own
+shard of the batch (weak scaling) and the small weight gradients are
+all-reduced over NCCL inside the step, as in data-parallel training.
+
+``--impl reference`` times the CPU restatement of the reference's unfused
+PyTorch path (the oracle) on the host cores; it is the only place besides the
+``cpu_baseline`` leg where this file executes anything under ``oracle/``.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CELLS = {2: (1, 2), 4: (2, 2), 8: (2, 4), 16: (4, 4)}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--slots", type=int, default=4, help="streams per token n (2/4/8/16)")
+    ap.add_argument("--channels", type=int, default=768)
+    ap.add_argument("--log2-tokens", type=int, default=20, help="batch x tokens per GPU = 2**this")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    return ap.parse_args()
+
+
+def algorithmic_units(slots: int) -> dict:
+    return {"read_fwd": slots + 1, "write_fwd": 2 * slots + 1, "read_bwd": 2 * slots + 1, "write_bwd": slots + 2}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc, self.thread = index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()           # the exact child we started
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        if self.thread:
+            self.thread.join(timeout=2)
+        clocks, reasons, mx = [], set(), None
+        for parts in self.samples:
+            try:
+                clocks.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(self.NAMES, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def make_inputs(batch, grid, slots, channels, dtype, device, seed=0):
+    kh, kw = CELLS[slots]
+    gen = torch.Generator(device=device).manual_seed(seed)
+
+    def randn(*shape, mean=0.0, std=1.0):
+        t = torch.empty(*shape, device=device, dtype=dtype)
+        return t.normal_(mean, std, generator=gen)
+
+    return dict(
+        x=randn(batch, grid * kh, grid * kw, channels),
+        dz=randn(batch, grid * grid, channels),
+        gz=randn(batch, grid * grid, channels),
+        gy=randn(batch, grid * kh, grid * kw, channels),
+        alpha=randn(1, channels, slots, mean=1.0 / slots, std=0.02),
+        beta=randn(1, channels, slots, mean=1.0 / slots, std=0.02),
+    )
+
+
+# ------------------------------------------------------------------------------------------ ours
+class DevicePath:
+    """The four hot-path launches on resident tensors, straight through the C ABI."""
+
+    def __init__(self, inp, batch, grid, slots, channels, dtype):
+        from residual_stream_burden_b200 import _lib
+        self.lib, self._lib = _lib.lib, _lib
+        self.inp = inp
+        kh, kw = CELLS[slots]
+        self.geom = (batch, grid, kh, kw, channels)
+        self.dt = _lib.BF16 if dtype == torch.bfloat16 else _lib.F32
+        dev = inp["x"].device
+        self.z = torch.empty_like(inp["dz"])
+        self.y = torch.empty_like(inp["x"])
+        self.dx = torch.empty_like(inp["x"])
+        self.ddz = torch.empty_like(inp["dz"])
+        self.dalpha = torch.empty(1, channels, slots, device=dev, dtype=torch.float32)
+        self.dbeta = torch.empty(1, channels, slots, device=dev, dtype=torch.float32)
+        nbytes = self.lib.sihc_wgrad_workspace_bytes(1, batch, grid, kh, kw, channels, self.dt)
+        self.ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+        pa = _lib.ptr_array
+        self.p_z, self.p_dz = pa([self.z.data_ptr()]), pa([inp["dz"].data_ptr()])
+        self.p_gz, self.p_ddz = pa([inp["gz"].data_ptr()]), pa([self.ddz.data_ptr()])
+        self.stream = torch.cuda.current_stream().cuda_stream
+
+    def read_fwd(self):
+        i = self.inp
+        self._lib.check(self.lib.sihc_read_fwd(i["x"].data_ptr(), i["alpha"].data_ptr(), self.p_z, 1, *self.geom,
+                                               self.dt, self.dt, self.stream), "read_fwd")
+
+    def write_fwd(self):
+        i = self.inp
+        self._lib.check(self.lib.sihc_write_fwd(i["x"].data_ptr(), self.p_dz, i["beta"].data_ptr(), self.y.data_ptr(),
+                                                1, *self.geom, self.dt, self.dt, self.stream), "write_fwd")
+
+    def read_bwd(self):
+        i = self.inp
+        self._lib.check(self.lib.sihc_read_bwd(i["x"].data_ptr(), self.p_gz, i["alpha"].data_ptr(), self.dx.data_ptr(),
+                                               self.dalpha.data_ptr(), self.ws.data_ptr(), self.ws.numel(), 1,
+                                               *self.geom, self.dt, self.dt, self.stream), "read_bwd")
+
+    def write_bwd(self):
+        i = self.inp
+        self._lib.check(self.lib.sihc_write_bwd(i["gy"].data_ptr(), self.p_dz, i["beta"].data_ptr(), self.p_ddz,
+                                                self.dbeta.data_ptr(), self.ws.data_ptr(), self.ws.numel(), 1,
+                                                *self.geom, self.dt, self.dt, self.stream), "write_bwd")
+
+    STAGES = ("read_fwd", "write_fwd", "read_bwd", "write_bwd")
+
+
+def run_e2e(args, batch, grid, slots, channels, dtype, device, steps):
+    """The same step through the public autograd API with HOST buffers.
+
+    The per-GPU batch is streamed in chunks: each chunk's inputs are copied from
+    pinned host memory, the four passes run through ``sihc_read`` / ``sihc_write``
+    and autograd, and every result is copied back to pinned host memory.  Two
+    CUDA streams overlap the copies of one chunk with the kernels of the other.
+    """
+    import residual_stream_burden_b200 as R
+    kh, kw = CELLS[slots]
+    chunk = min(batch, 256)
+    nchunks = (batch + chunk - 1) // chunk
+    gen = torch.Generator().manual_seed(1)
+    ibits = torch.int16 if dtype == torch.bfloat16 else torch.int32
+
+    def host(*shape):
+        # pinned buffer filled with small finite values (random low bit patterns: cheap to generate)
+        t = torch.empty(*shape, dtype=dtype).pin_memory()
+        t.view(ibits).random_(-8000, 8000, generator=gen)
+        return t
+
+    carrier, work = (chunk, grid * kh, grid * kw, channels), (chunk, grid * grid, channels)
+    h_in = dict(x=host(*carrier), dz=host(*work), gz=host(*work), gy=host(*carrier))
+    h_out = [dict(z=host(*work), y=host(*carrier), dx=host(*carrier), ddz=host(*work)) for _ in range(2)]
+    h_dw = torch.empty(2, channels, slots, dtype=dtype).pin_memory()
+    alpha = torch.full((channels, slots), 1.0 / slots, device=device, dtype=dtype).requires_grad_()
+    beta = torch.full((channels, slots), 1.0, device=device, dtype=dtype).requires_grad_()
+    streams = [torch.cuda.Stream(device=device) for _ in range(2)]
+    d_in = [{k: torch.empty_like(v, device=device) for k, v in h_in.items()} for _ in range(2)]
+    sums = [torch.zeros(2, channels, slots, device=device, dtype=torch.float32) for _ in range(2)]
+    esize = h_in["x"].element_size()
+    h2d = sum(v.numel() for v in h_in.values()) * esize * nchunks
+    d2h = (sum(v.numel() for v in h_out[0].values()) * nchunks + h_dw.numel()) * esize
+
+    def step():
+        main_stream = torch.cuda.current_stream()
+        for si, s in enumerate(streams):
+            s.wait_stream(main_stream)
+            with torch.cuda.stream(s):
+                sums[si].zero_()
+        for ci in range(nchunks):
+            si = ci % 2
+            buf, out = d_in[si], h_out[si]
+            with torch.cuda.stream(streams[si]):
+                for k in h_in:
+                    buf[k].copy_(h_in[k], non_blocking=True)
+                x = buf["x"].detach().requires_grad_()
+                dz = buf["dz"].detach().requires_grad_()
+                z = R.sihc_read(x, alpha)
+                y = R.sihc_write(x, dz, beta)
+                dx, da = torch.autograd.grad(z, (x, alpha), buf["gz"])
+                ddz, db = torch.autograd.grad(y, (dz, beta), buf["gy"])
+                out["z"].copy_(z, non_blocking=True)
+                out["y"].copy_(y, non_blocking=True)
+                out["dx"].copy_(dx, non_blocking=True)
+                out["ddz"].copy_(ddz, non_blocking=True)
+                sums[si][0].add_(da)
+                sums[si][1].add_(db)
+        for s in streams:
+            main_stream.wait_stream(s)
+        h_dw.copy_((sums[0] + sums[1]).to(dtype), non_blocking=True)
+
+    step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    seconds = (time.perf_counter() - t0) / steps
+    return seconds, h2d, d2h, chunk
+
+
+# ------------------------------------------------------------------------------------------ CPU
+def cpu_step_factory(batch, grid, slots, channels, dtype):
+    """The reference's unfused eager path on the host: read_torch/write_torch + autograd."""
+    from oracle import sihc_oracle as O
+    inp = make_inputs(batch, grid, slots, channels, dtype, torch.device("cpu"))
+
+    def step():
+        x = inp["x"].clone().requires_grad_()
+        alpha = inp["alpha"][0].clone().requires_grad_()
+        beta = inp["beta"][0].clone().requires_grad_()
+        dz = inp["dz"].clone().requires_grad_()
+        z = O.read(x, alpha)
+        y = O.write(x, [dz], [beta])
+        torch.autograd.grad(z, (x, alpha), inp["gz"])
+        torch.autograd.grad(y, (dz, beta), inp["gy"])
+
+    return step
+
+
+def time_cpu(batch, grid, slots, channels, dtype, reps, warm=1):
+    torch.set_num_threads(os.cpu_count() or 1)
+    step = cpu_step_factory(batch, grid, slots, channels, dtype)
+    for _ in range(warm):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        step()
+    return (time.perf_counter() - t0) / reps
+
+
+def main():
+    args = parse_args()
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    esize = 2 if dtype == torch.bfloat16 else 4
+    slots, channels, grid = args.slots, args.channels, 16
+    tokens = 1 << args.log2_tokens
+    batch = max(1, tokens // (grid * grid))
+    tokens = batch * grid * grid
+    units = algorithmic_units(slots)
+    step_bytes = sum(units.values()) * tokens * channels * esize
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    workload = (f"SiHC read+write fwd+bwd, single event, n={slots} streams, width {channels}, "
+                f"batch x tokens = 2^{args.log2_tokens} per GPU ({batch} x {grid * grid}), {args.dtype}")
+    config = {"workload": workload, "slots": slots, "channels": channels, "tokens_per_gpu": tokens,
+              "l2": "inputs larger than L2 (no flush needed)", "parallelism": f"dp{world}"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cores = os.cpu_count() or 1
+        sample_batch = 32
+        sample_tokens = sample_batch * grid * grid
+        for _ in range(max(0, min(args.warmup, 1))):
+            time_cpu(sample_batch, grid, slots, channels, dtype, 1, warm=0)
+        sec = time_cpu(sample_batch, grid, slots, channels, dtype, max(1, min(args.steps, 5)), warm=0)
+        gbs = sum(units.values()) * sample_tokens * channels * esize / sec / 1e9
+        sample = f"{sample_batch} images ({sample_tokens} tokens) of the workload per step, torch eager on CPU"
+        line = {"impl": "reference", "metric": "sihc_read_write_fwd_bwd_bandwidth", "value": gbs, "unit": "GB/s",
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.dtype,
+                "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+                "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    from residual_stream_burden_b200 import _lib
+
+    inp = make_inputs(batch, grid, slots, channels, dtype, device, seed=rank)
+    path = DevicePath(inp, batch, grid, slots, channels, dtype)
+    grads = torch.empty(2, channels, slots, device=device, dtype=torch.float32)
+
+    def step(events=None):
+        for k, name in enumerate(DevicePath.STAGES):
+            if events is not None:
+                events[k][0].record()
+            getattr(path, name)()
+            if events is not None:
+                events[k][1].record()
+        if world > 1:       # data-parallel exchange of the small weight gradients
+            grads[0].copy_(path.dalpha[0])
+            grads[1].copy_(path.dbeta[0])
+            dist.all_reduce(grads)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    per_kernel = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(4)]
+                  for _ in range(args.steps)]
+    launches0 = _lib.launch_count()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for k in range(args.steps):
+        step(per_kernel[k])
+    end.record()
+    torch.cuda.synchronize()
+    launches = _lib.launch_count() - launches0
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = start.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    kernel_ms = {name: statistics.mean(ev[k][0].elapsed_time(ev[k][1]) for ev in per_kernel)
+                 for k, name in enumerate(DevicePath.STAGES)}
+    peak, peak_kind = load_peaks()
+    kernels = {}
+    for name in DevicePath.STAGES:
+        nbytes = units[name] * tokens * channels * esize
+        gbs = nbytes / (kernel_ms[name] * 1e-3) / 1e9
+        kernels[name] = {"ms": round(kernel_ms[name], 4), "GB/s": round(gbs, 1), "frac": round(gbs / peak, 4)}
+    dominant = max(DevicePath.STAGES, key=lambda n: kernel_ms[n])
+    dom_bytes = units[dominant] * tokens * channels * esize
+    achieved = dom_bytes / (kernel_ms[dominant] * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": dominant, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "peak_source": f"{peak_kind} copy bandwidth",
+                "algorithmic_bytes_per_launch": dom_bytes, "traffic": None,
+                "all_kernels": kernels, "step_frac_of_peak": round(value / world / peak, 4)}
+
+    e2e = None
+    if not args.no_e2e:
+        sec, h2d, d2h, chunk = run_e2e(args, batch, grid, slots, channels, dtype, device, args.e2e_steps)
+        if world > 1:
+            t = torch.tensor([sec], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec = float(t.item())
+        e2e = {"value": round(world * step_bytes / sec / 1e9, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": round(sec * 1e3, 2),
+               "api": "sihc_read / sihc_write + torch.autograd, pinned host buffers, chunks of %d images" % chunk}
+
+    cpu = None
+    if rank == 0 and not args.no_cpu and world == 1:
+        sample_batch = 32
+        sec = time_cpu(sample_batch, grid, slots, channels, dtype, reps=3)
+        sample_tokens = sample_batch * grid * grid
+        cpu = {"value": round(sum(units.values()) * sample_tokens * channels * esize / sec / 1e9, 3), "unit": "GB/s",
+               "cores": os.cpu_count() or 1, "kind": "port",
+               "sample": f"{sample_batch} images ({sample_tokens} tokens) of the workload, torch eager on CPU, "
+                         f"{sec * 1e3:.0f} ms per pass"}
+
+    if rank == 0:
+        line = {"metric": "sihc_read_write_fwd_bwd_bandwidth", "value": round(value, 1), "unit": "GB/s",
+                "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "config": config,
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+                "clocks": clocks}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,161 @@
+/*
+ * sihc_b200 — C ABI of the B200 (sm_100a) SiHC hyper-connection routing library.
+ *
+ * This is the drop-in boundary for the reference's fused routing operators.
+ * Every entry point is plain C: raw device pointers, sizes, a CUDA stream passed
+ * as `void*` (a `cudaStream_t`), and an `int` status.  The library allocates no
+ * memory, keeps no per-call state, never synchronises the device and launches
+ * only on the stream it is given, so it may be called from the autograd worker
+ * thread, from compiled graphs and under stream capture.
+ *
+ * Geometry shared by all carrier operators (reference: `_high_offsets`,
+ * sihc/models/sihc/sublayer_kernels.py:21-25 and `_geometry`, :180-193):
+ *   carrier  X  : NHWC, packed, [batch, grid*kh, grid*kw, channels]
+ *   workspace z : packed, [batch, grid*grid, channels]
+ *   weights     : packed, [events, channels, slots], slots = kh*kw
+ *   token m = (b, wy, wx) owns carrier pixels (wy*kh+uy, wx*kw+ux); slot s = uy*kw+ux.
+ * Supported cells: (kh,kw) in {(1,2),(2,2),(2,4),(4,4)}  -> slots in {2,4,8,16}.
+ * The reference supports (2,2) and (4,4) only; the others are this library's extension.
+ *
+ * dtype codes: SIHC_F32 = 0, SIHC_BF16 = 1.  `dtype` is the storage type of the
+ * carrier and workspace tensors; `wdtype` is the storage type of the weight
+ * tensor (alpha / beta / gamma) and must be `dtype` or SIHC_F32.  All arithmetic
+ * accumulates in fp32 and rounds once when storing.
+ *
+ * Pointer arrays (`const void* const*`) are HOST arrays of `events` device
+ * pointers; they are copied by value into the kernel parameters (the analogue
+ * of the reference's tuple-of-pointers kernels).
+ *
+ * Status: 0 success; negative = invalid argument (see sihc_status_string);
+ * positive = a cudaError_t reported by the launch.
+ */
+#ifndef SIHC_B200_H_
+#define SIHC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SIHC_F32 0
+#define SIHC_BF16 1
+#define SIHC_MAX_EVENTS 24
+
+#define SIHC_OK 0
+#define SIHC_ERR_NULL (-1)        /* a required pointer is null */
+#define SIHC_ERR_DTYPE (-2)       /* unsupported dtype / wdtype combination */
+#define SIHC_ERR_EVENTS (-3)      /* events outside 1..SIHC_MAX_EVENTS */
+#define SIHC_ERR_CELL (-4)        /* (kh,kw) not a supported cell */
+#define SIHC_ERR_SHAPE (-5)       /* non-positive or overflowing batch/grid/channels */
+#define SIHC_ERR_WORKSPACE (-6)   /* workspace missing, misaligned or too small */
+#define SIHC_ERR_ALIGN (-7)       /* a tensor pointer is not aligned to its element size */
+#define SIHC_ERR_CAPACITY (-8)    /* size beyond a built-in fixed capacity */
+
+/* Library ABI version (bumped on any signature change). */
+int sihc_version(void);
+
+/* Human-readable text for a status returned by any entry point. */
+const char* sihc_status_string(int status);
+
+/*
+ * Stage read, forward.  out[l][m,c] = sum_s alpha[l,c,s] * X[m,s,c]  for l < events.
+ * Replaces `sublayer_read` + `_read` / `_read_bf16_mma`
+ * (sihc/models/sihc/sublayer_kernels.py:219-232, :28-79) and, with events == 1,
+ * `read_torch` (sihc/bench/fusion_controls.py:14-20).
+ */
+int sihc_read_fwd(const void* x, const void* alpha, void* const* out, int events,
+                  int64_t batch, int grid, int kh, int kw, int channels,
+                  int dtype, int wdtype, void* stream);
+
+/*
+ * Stage write, forward.  y[m,s,c] = (x ? x[m,s,c] : 0) + sum_l beta[l,c,s] * dz[l][m,c].
+ * Replaces `sublayer_write` / `_write_impl` + `_write` / `_write_bf16_mma`
+ * (sihc/models/sihc/sublayer_kernels.py:246-258, :290-292, :82-127); `x == NULL`
+ * is the reference's `add_x=False` (the read's carrier gradient, :284); events == 1
+ * is `write_torch` (sihc/bench/fusion_controls.py:23-31).  `y` must not alias `x`.
+ */
+int sihc_write_fwd(const void* x, const void* const* dz, const void* beta, void* y, int events,
+                   int64_t batch, int grid, int kh, int kw, int channels,
+                   int dtype, int wdtype, void* stream);
+
+/*
+ * Bytes of scratch the two backward entry points below need for `events` events
+ * on this geometry (per-block partial sums of the weight gradients).  The
+ * scratch needs no initialisation and holds nothing between calls.
+ */
+size_t sihc_wgrad_workspace_bytes(int events, int64_t batch, int grid, int kh, int kw,
+                                  int channels, int dtype);
+
+/*
+ * Stage read, backward (both adjoints in one call).
+ *   dx[m,s,c]       = sum_l alpha[l,c,s] * g[l][m,c]
+ *   dalpha[l,c,s]   = sum_m X[m,s,c] * g[l][m,c]          (fp32, [events,channels,slots])
+ * Replaces `_read_backward` (sihc/models/sihc/sublayer_kernels.py:280-284), i.e.
+ * `_write_impl(..., add_x=False)` plus `_weights_backward` (:261-273) with its
+ * `_weight_grad*` kernels (:130-177).  A NULL entry g[l] is an unused read output:
+ * it adds nothing to dx and leaves dalpha[l] exactly zero (the reference
+ * materialises zeros, :283).  `dx` or `dalpha` may be NULL to skip that output.
+ * The reduction over tokens is deterministic (no atomics): fixed per-block
+ * partials in `workspace`, then a fixed-order finishing pass.
+ */
+int sihc_read_bwd(const void* x, const void* const* g, const void* alpha, void* dx, float* dalpha,
+                  void* workspace, size_t workspace_bytes, int events,
+                  int64_t batch, int grid, int kh, int kw, int channels,
+                  int dtype, int wdtype, void* stream);
+
+/*
+ * Stage write, backward w.r.t. the updates and beta (the carrier gradient of the
+ * write is `h` itself and needs no kernel).
+ *   ddz[l][m,c]     = sum_s beta[l,c,s] * h[m,s,c]
+ *   dbeta[l,c,s]    = sum_m dz[l][m,c] * h[m,s,c]         (fp32, [events,channels,slots])
+ * Replaces `_write_backward` (sihc/models/sihc/sublayer_kernels.py:300-303), i.e.
+ * `sublayer_read(grad, beta)` plus `_weights_backward(grad, updates, beta)`.
+ * `ddz` (the array) or `dbeta` may be NULL to skip that output.
+ */
+int sihc_write_bwd(const void* h, const void* const* dz, const void* beta, void* const* ddz,
+                   float* dbeta, void* workspace, size_t workspace_bytes, int events,
+                   int64_t batch, int grid, int kh, int kw, int channels,
+                   int dtype, int wdtype, void* stream);
+
+/*
+ * Triangular accumulation, forward.  out = base + sum_{l<active} gamma[l,c] * dz[l].
+ * `tokens` = batch*grid*grid rows of `channels`; gamma is [active, channels] in `gdtype`.
+ * Replaces `sublayer_triangular` + `_triangular`
+ * (sihc/models/sihc/sublayer_kernels.py:337-352, :309-321) and `triangular_torch`
+ * (sihc/bench/fusion_controls.py:34-38).  active in 1..SIHC_MAX_EVENTS.
+ */
+int sihc_tri_fwd(const void* base, const void* const* dz, const void* gamma, void* out, int active,
+                 int64_t tokens, int channels, int dtype, int gdtype, void* stream);
+
+/* Scratch bytes for sihc_tri_bwd's deterministic dgamma reduction. */
+size_t sihc_tri_workspace_bytes(int active, int64_t tokens, int channels, int dtype);
+
+/*
+ * Triangular accumulation, backward.
+ *   ddz[l]       = grad * gamma[l]        (fp32 product, one rounding)   if ddz != NULL
+ *   dgamma[l,c]  = sum_m grad[m,c] * dz[l][m,c]   (fp32, [active,channels]) if dgamma != NULL
+ * Replaces `_tri_autograd` / `_tri_gamma_backward` + `_triangular_gamma_grad`
+ * (sihc/models/sihc/sublayer_kernels.py:369-379, :355-361, :324-334).
+ */
+int sihc_tri_bwd(const void* grad, const void* const* dz, const void* gamma, void* const* ddz,
+                 float* dgamma, void* workspace, size_t workspace_bytes, int active,
+                 int64_t tokens, int channels, int dtype, int gdtype, void* stream);
+
+/*
+ * Benchmark-only knob: override a launch parameter by name ("threads",
+ * "tokens_per_thread", "blocks_per_sm", ...); value <= 0 restores the default.
+ * Process-global and not thread-safe; never needed for correct results.
+ * Returns 0, or SIHC_ERR_NULL for an unknown name.  (Counterpart of the
+ * reference's `SIHC_*` environment tile overrides, sihc/models/sihc/kernels.py:19-23.)
+ */
+int sihc_tune(const char* name, int value);
+
+/* Number of kernel launches this library has issued in this process (for benches). */
+uint64_t sihc_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SIHC_B200_H_ */

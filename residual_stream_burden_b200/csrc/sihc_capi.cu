@@ -1,0 +1,331 @@
+// C ABI of the SiHC routing library: argument validation, vector-width
+// selection from sizes and pointer alignment, and the composition of kernels
+// behind each entry point.  Declarations and the reference symbols each entry
+// point replaces are in include/sihc_b200.h.
+#include "sihc_b200.h"
+
+#include <atomic>
+#include <cstring>
+
+#include "sihc_dispatch.cuh"
+
+namespace sihc {
+
+Tuning& tuning() {
+    static Tuning t;
+    return t;
+}
+
+int sm_count() {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+static std::atomic<uint64_t> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+
+uint32_t partial_blocks_bound(uint32_t M) {
+    const int cap = tuning().rbps > 0 ? tuning().rbps : 2;
+    uint32_t by_sm = static_cast<uint32_t>(sm_count()) * static_cast<uint32_t>(cap);
+    uint32_t by_tokens = (M + 63) / 64;      // a block should own at least 64 tokens
+    if (by_tokens < 1) by_tokens = 1;
+    return by_sm < by_tokens ? by_sm : by_tokens;
+}
+
+namespace {
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+inline size_t esize(int dtype) { return dtype == SIHC_BF16 ? 2 : 4; }
+
+int check_types(int dtype, int wdtype) {
+    if (dtype != SIHC_F32 && dtype != SIHC_BF16) return SIHC_ERR_DTYPE;
+    if (wdtype != dtype && wdtype != SIHC_F32) return SIHC_ERR_DTYPE;
+    return SIHC_OK;
+}
+
+int slots_of(int kh, int kw) {
+    if (kh == 1 && kw == 2) return 2;
+    if (kh == 2 && kw == 2) return 4;
+    if (kh == 2 && kw == 4) return 8;
+    if (kh == 4 && kw == 4) return 16;
+    return 0;
+}
+
+// Validate the carrier geometry and fill everything of Problem but V.
+int make_problem(Problem& pb, int events, int64_t batch, int grid, int kh, int kw, int channels, int dtype,
+                 int wdtype, void* stream) {
+    if (int st = check_types(dtype, wdtype)) return st;
+    if (events < 1 || events > SIHC_MAX_EVENTS) return SIHC_ERR_EVENTS;
+    const int S = slots_of(kh, kw);
+    if (S == 0) return SIHC_ERR_CELL;
+    if (batch < 1 || grid < 1 || channels < 1) return SIHC_ERR_SHAPE;
+    const int64_t tokens = batch * grid * grid;
+    if (grid > 65535 || tokens >= (int64_t(1) << 31) || channels > (1 << 24)) return SIHC_ERR_SHAPE;
+    pb.dtype = static_cast<DType>(dtype);
+    pb.wdtype = static_cast<DType>(wdtype);
+    pb.E = events; pb.S = S;
+    pb.M = static_cast<uint32_t>(tokens); pb.g = static_cast<uint32_t>(grid); pb.C = static_cast<uint32_t>(channels);
+    pb.V = 1;
+    pb.stream = static_cast<cudaStream_t>(stream);
+    return SIHC_OK;
+}
+
+// Tracks the widest vector access every pointer of a call allows.
+struct VecChoice {
+    int full;           // candidate channels per thread
+    size_t ebytes;
+    bool ok = true;
+    bool elem_ok = true;
+    VecChoice(int full_, size_t ebytes_, uint32_t C) : full(full_), ebytes(ebytes_) {
+        const int cap = tuning().maxvec_bytes;
+        if (cap > 0 && static_cast<size_t>(full) * ebytes > static_cast<size_t>(cap)) ok = false;
+        if (C % static_cast<uint32_t>(full) != 0) ok = false;
+    }
+    void act(const void* p) {            // activation tensor (may be null = absent)
+        if (!p) return;
+        if (!aligned(p, ebytes)) elem_ok = false;
+        if (!aligned(p, static_cast<size_t>(full) * ebytes)) ok = false;
+    }
+    void weight(const void* p, size_t wbytes) {
+        if (!p) return;
+        if (!aligned(p, wbytes)) elem_ok = false;
+        if (!aligned(p, 16)) ok = false;
+    }
+    int V() const { return ok ? full : 1; }
+};
+
+int status_of(cudaError_t e) { return e == cudaSuccess ? SIHC_OK : static_cast<int>(e); }
+
+int check_workspace(const void* ws, size_t have, size_t need) {
+    if (need == 0) return SIHC_OK;
+    if (ws == nullptr || !aligned(ws, 16) || have < need) return SIHC_ERR_WORKSPACE;
+    return SIHC_OK;
+}
+
+}  // namespace
+}  // namespace sihc
+
+using namespace sihc;
+
+extern "C" {
+
+int sihc_version(void) { return 1; }
+
+const char* sihc_status_string(int status) {
+    switch (status) {
+        case SIHC_OK: return "ok";
+        case SIHC_ERR_NULL: return "a required pointer is null";
+        case SIHC_ERR_DTYPE: return "unsupported dtype (fp32/bf16 activations; weights in the activation dtype or fp32)";
+        case SIHC_ERR_EVENTS: return "event count outside 1..24";
+        case SIHC_ERR_CELL: return "unsupported slot grid (kh,kw); supported: (1,2) (2,2) (2,4) (4,4)";
+        case SIHC_ERR_SHAPE: return "batch, grid and channels must be positive and tokens must fit 31 bits";
+        case SIHC_ERR_WORKSPACE: return "workspace missing, not 16-byte aligned, or smaller than sihc_*_workspace_bytes";
+        case SIHC_ERR_ALIGN: return "a tensor pointer is not aligned to its element size";
+        case SIHC_ERR_CAPACITY: return "size exceeds the fixed capacity of this entry point";
+        default: break;
+    }
+    if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+    return "unknown status";
+}
+
+int sihc_tune(const char* name, int value) {
+    if (!name) return SIHC_ERR_NULL;
+    Tuning& t = tuning();
+    if (value < 0) value = 0;
+    if (!std::strcmp(name, "threads")) t.threads = value;
+    else if (!std::strcmp(name, "tokens_per_thread")) t.tt = value;
+    else if (!std::strcmp(name, "blocks_per_sm")) t.bps = value;
+    else if (!std::strcmp(name, "partial_blocks_per_sm")) t.rbps = value;
+    else if (!std::strcmp(name, "max_vector_bytes")) t.maxvec_bytes = value;
+    else return SIHC_ERR_NULL;
+    return SIHC_OK;
+}
+
+uint64_t sihc_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int sihc_read_fwd(const void* x, const void* alpha, void* const* out, int events, int64_t batch, int grid, int kh,
+                  int kw, int channels, int dtype, int wdtype, void* stream) {
+    Problem pb;
+    if (int st = make_problem(pb, events, batch, grid, kh, kw, channels, dtype, wdtype, stream)) return st;
+    if (!x || !alpha || !out) return SIHC_ERR_NULL;
+    VecChoice vc(vec_width(pb.dtype, pb.S), esize(dtype), pb.C);
+    vc.act(x); vc.weight(alpha, esize(wdtype));
+    bool any = false;
+    for (int l = 0; l < events; ++l) { vc.act(out[l]); any = any || out[l]; }
+    if (!any) return SIHC_ERR_NULL;
+    if (events == 1 && !out[0]) return SIHC_ERR_NULL;
+    if (!vc.elem_ok) return SIHC_ERR_ALIGN;
+    pb.V = vc.V();
+    return status_of(launch_read_fwd(pb, x, alpha, out));
+}
+
+int sihc_write_fwd(const void* x, const void* const* dz, const void* beta, void* y, int events, int64_t batch,
+                   int grid, int kh, int kw, int channels, int dtype, int wdtype, void* stream) {
+    Problem pb;
+    if (int st = make_problem(pb, events, batch, grid, kh, kw, channels, dtype, wdtype, stream)) return st;
+    if (!dz || !beta || !y) return SIHC_ERR_NULL;
+    VecChoice vc(vec_width(pb.dtype, pb.S), esize(dtype), pb.C);
+    vc.act(x); vc.act(y); vc.weight(beta, esize(wdtype));
+    for (int l = 0; l < events; ++l) vc.act(dz[l]);
+    if (!vc.elem_ok) return SIHC_ERR_ALIGN;
+    pb.V = vc.V();
+    return status_of(launch_write_fwd(pb, x, dz, beta, y));
+}
+
+size_t sihc_wgrad_workspace_bytes(int events, int64_t batch, int grid, int kh, int kw, int channels, int dtype) {
+    Problem pb;
+    if (make_problem(pb, events, batch, grid, kh, kw, channels, dtype, dtype, nullptr)) return 0;
+    return static_cast<size_t>(partial_blocks_bound(pb.M)) * static_cast<size_t>(events) * pb.S * pb.C * sizeof(float);
+}
+
+int sihc_read_bwd(const void* x, const void* const* g, const void* alpha, void* dx, float* dalpha, void* workspace,
+                  size_t workspace_bytes, int events, int64_t batch, int grid, int kh, int kw, int channels,
+                  int dtype, int wdtype, void* stream) {
+    Problem pb;
+    if (int st = make_problem(pb, events, batch, grid, kh, kw, channels, dtype, wdtype, stream)) return st;
+    if (!x || !g || !alpha) return SIHC_ERR_NULL;
+    if (!dx && !dalpha) return SIHC_OK;
+    VecChoice vc(vec_width(pb.dtype, pb.S), esize(dtype), pb.C);
+    vc.act(x); vc.act(dx); vc.weight(alpha, esize(wdtype));
+    bool any = false;
+    for (int l = 0; l < events; ++l) { vc.act(g[l]); any = any || g[l]; }
+    if (!vc.elem_ok || (dalpha && !aligned(dalpha, 4))) return SIHC_ERR_ALIGN;
+    pb.V = vc.V();
+    const size_t carrier_bytes = static_cast<size_t>(pb.M) * pb.S * pb.C * esize(dtype);
+    const size_t wbytes = static_cast<size_t>(events) * pb.C * pb.S * sizeof(float);
+    if (!any) {   // no output of the read was used
+        cudaError_t e = cudaSuccess;
+        if (dx) e = cudaMemsetAsync(dx, 0, carrier_bytes, pb.stream);
+        if (e == cudaSuccess && dalpha) e = cudaMemsetAsync(dalpha, 0, wbytes, pb.stream);
+        return status_of(e);
+    }
+    if (dalpha) {
+        const size_t need = sihc_wgrad_workspace_bytes(events, batch, grid, kh, kw, channels, dtype);
+        if (int st = check_workspace(workspace, workspace_bytes, need)) return st;
+    }
+    float* partial = dalpha ? static_cast<float*>(workspace) : nullptr;
+    uint32_t blocks = 0;
+    cudaError_t e;
+    if (events == 1) {
+        e = launch_read_bwd1(pb, x, g[0], alpha, dx, partial, &blocks);
+    } else {
+        e = cudaSuccess;
+        if (dx) e = launch_write_fwd(pb, nullptr, g, alpha, dx);
+        if (e == cudaSuccess && dalpha) e = launch_wgrad(pb, x, g, partial, &blocks);
+    }
+    if (e == cudaSuccess && dalpha)
+        e = launch_finish(partial, dalpha, blocks, static_cast<uint32_t>(events) * pb.S, pb.C, pb.S, pb.stream);
+    return status_of(e);
+}
+
+int sihc_write_bwd(const void* h, const void* const* dz, const void* beta, void* const* ddz, float* dbeta,
+                   void* workspace, size_t workspace_bytes, int events, int64_t batch, int grid, int kh, int kw,
+                   int channels, int dtype, int wdtype, void* stream) {
+    Problem pb;
+    if (int st = make_problem(pb, events, batch, grid, kh, kw, channels, dtype, wdtype, stream)) return st;
+    if (!h || !beta) return SIHC_ERR_NULL;
+    if (dbeta && !dz) return SIHC_ERR_NULL;
+    bool want_ddz = false;
+    if (ddz) for (int l = 0; l < events; ++l) want_ddz = want_ddz || ddz[l];
+    if (!want_ddz && !dbeta) return SIHC_OK;
+    VecChoice vc(vec_width(pb.dtype, pb.S), esize(dtype), pb.C);
+    vc.act(h); vc.weight(beta, esize(wdtype));
+    for (int l = 0; l < events; ++l) {
+        if (dbeta) { if (!dz[l]) return SIHC_ERR_NULL; vc.act(dz[l]); }
+        if (ddz) vc.act(ddz[l]);
+    }
+    if (!vc.elem_ok || (dbeta && !aligned(dbeta, 4))) return SIHC_ERR_ALIGN;
+    pb.V = vc.V();
+    if (dbeta) {
+        const size_t need = sihc_wgrad_workspace_bytes(events, batch, grid, kh, kw, channels, dtype);
+        if (int st = check_workspace(workspace, workspace_bytes, need)) return st;
+    }
+    float* partial = dbeta ? static_cast<float*>(workspace) : nullptr;
+    uint32_t blocks = 0;
+    cudaError_t e;
+    if (events == 1) {
+        e = launch_write_bwd1(pb, h, dbeta ? dz[0] : nullptr, beta, want_ddz ? ddz[0] : nullptr, partial, &blocks);
+    } else {
+        e = cudaSuccess;
+        if (want_ddz) e = launch_read_fwd(pb, h, beta, ddz);
+        if (e == cudaSuccess && dbeta) e = launch_wgrad(pb, h, dz, partial, &blocks);
+    }
+    if (e == cudaSuccess && dbeta)
+        e = launch_finish(partial, dbeta, blocks, static_cast<uint32_t>(events) * pb.S, pb.C, pb.S, pb.stream);
+    return status_of(e);
+}
+
+static int make_tri_problem(Problem& pb, int active, int64_t tokens, int channels, int dtype, int gdtype, void* stream) {
+    if (int st = check_types(dtype, gdtype)) return st;
+    if (active < 1 || active > SIHC_MAX_EVENTS) return SIHC_ERR_EVENTS;
+    if (tokens < 1 || channels < 1 || tokens >= (int64_t(1) << 31) || channels > (1 << 24)) return SIHC_ERR_SHAPE;
+    pb.dtype = static_cast<DType>(dtype);
+    pb.wdtype = static_cast<DType>(gdtype);
+    pb.E = active; pb.S = 0;
+    pb.M = static_cast<uint32_t>(tokens); pb.g = 1; pb.C = static_cast<uint32_t>(channels);
+    pb.V = 1;
+    pb.stream = static_cast<cudaStream_t>(stream);
+    return SIHC_OK;
+}
+
+int sihc_tri_fwd(const void* base, const void* const* dz, const void* gamma, void* out, int active, int64_t tokens,
+                 int channels, int dtype, int gdtype, void* stream) {
+    Problem pb;
+    if (int st = make_tri_problem(pb, active, tokens, channels, dtype, gdtype, stream)) return st;
+    if (!base || !dz || !gamma || !out) return SIHC_ERR_NULL;
+    VecChoice vc(vec_width(pb.dtype, 0), esize(dtype), pb.C);
+    vc.act(base); vc.act(out); vc.weight(gamma, esize(gdtype));
+    // gamma rows are C elements apart: vector loads need every row 16-byte aligned
+    if ((static_cast<size_t>(pb.C) * esize(gdtype)) % 16 != 0) vc.ok = false;
+    for (int l = 0; l < active; ++l) { if (!dz[l]) return SIHC_ERR_NULL; vc.act(dz[l]); }
+    if (!vc.elem_ok) return SIHC_ERR_ALIGN;
+    pb.V = vc.V();
+    return status_of(launch_tri_fwd(pb, base, dz, gamma, out));
+}
+
+size_t sihc_tri_workspace_bytes(int active, int64_t tokens, int channels, int dtype) {
+    Problem pb;
+    if (make_tri_problem(pb, active, tokens, channels, dtype, dtype, nullptr)) return 0;
+    return static_cast<size_t>(partial_blocks_bound(pb.M)) * static_cast<size_t>(active) * pb.C * sizeof(float);
+}
+
+int sihc_tri_bwd(const void* grad, const void* const* dz, const void* gamma, void* const* ddz, float* dgamma,
+                 void* workspace, size_t workspace_bytes, int active, int64_t tokens, int channels, int dtype,
+                 int gdtype, void* stream) {
+    Problem pb;
+    if (int st = make_tri_problem(pb, active, tokens, channels, dtype, gdtype, stream)) return st;
+    if (!grad || !gamma) return SIHC_ERR_NULL;
+    if (dgamma && !dz) return SIHC_ERR_NULL;
+    bool want_ddz = false;
+    if (ddz) for (int l = 0; l < active; ++l) want_ddz = want_ddz || ddz[l];
+    if (!want_ddz && !dgamma) return SIHC_OK;
+    VecChoice vc(vec_width(pb.dtype, 0), esize(dtype), pb.C);
+    vc.act(grad); vc.weight(gamma, esize(gdtype));
+    if ((static_cast<size_t>(pb.C) * esize(gdtype)) % 16 != 0) vc.ok = false;
+    for (int l = 0; l < active; ++l) {
+        if (dgamma) { if (!dz[l]) return SIHC_ERR_NULL; vc.act(dz[l]); }
+        if (ddz) vc.act(ddz[l]);
+    }
+    if (!vc.elem_ok || (dgamma && !aligned(dgamma, 4))) return SIHC_ERR_ALIGN;
+    pb.V = vc.V();
+    if (dgamma) {
+        const size_t need = sihc_tri_workspace_bytes(active, tokens, channels, dtype);
+        if (int st = check_workspace(workspace, workspace_bytes, need)) return st;
+    }
+    float* partial = dgamma ? static_cast<float*>(workspace) : nullptr;
+    uint32_t blocks = 0;
+    const void* no_dz[SIHC_MAX_EVENTS] = {};
+    cudaError_t e = launch_tri_bwd(pb, grad, dz ? dz : no_dz, gamma, want_ddz ? ddz : nullptr, partial, &blocks);
+    if (e == cudaSuccess && dgamma)
+        e = launch_finish(partial, dgamma, blocks, static_cast<uint32_t>(active), pb.C, 1, pb.stream);
+    return status_of(e);
+}
+
+}  // extern "C"

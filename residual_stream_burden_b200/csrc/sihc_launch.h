@@ -1,0 +1,84 @@
+// Internal host-side interface between the C ABI (sihc_capi.cu) and the kernel
+// translation units.  Not part of the public ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "sihc_common.cuh"
+
+namespace sihc {
+
+enum DType { kF32 = 0, kBF16 = 1 };
+
+// Tunable launch parameters (defaults chosen from measurements on B200).
+struct Tuning {
+    int threads = 0;        // target threads per block (0: per-kernel default)
+    int tt = 0;             // tokens per thread per tile (0: per-kernel default)
+    int bps = 0;            // blocks per SM cap for streaming kernels (0: occupancy)
+    int rbps = 0;           // blocks per SM for kernels that emit partial sums (0: default 2)
+    int maxvec_bytes = 0;   // cap on the vector width in bytes (0: 16)
+};
+Tuning& tuning();
+int sm_count();
+void count_launch(int n = 1);
+
+// Problem description after validation.
+struct Problem {
+    DType dtype, wdtype;
+    int E;              // events (or active prefix for triangular)
+    int S;              // slots (0 for triangular)
+    uint32_t M, g, C;
+    int V;              // channels per thread chosen by the C ABI from size/alignment
+    cudaStream_t stream;
+};
+
+// Upper bound on the number of partial-sum blocks a reduction kernel will use.
+uint32_t partial_blocks_bound(uint32_t M);
+
+cudaError_t launch_read_fwd(const Problem& pb, const void* x, const void* alpha, void* const* out);
+cudaError_t launch_write_fwd(const Problem& pb, const void* x, const void* const* dz, const void* beta, void* y);
+// Fused single-event adjoints; `partial` receives [P][S][C] fp32 rows, *blocks = P.
+cudaError_t launch_read_bwd1(const Problem& pb, const void* x, const void* g, const void* alpha, void* dx,
+                             float* partial, uint32_t* blocks);
+cudaError_t launch_write_bwd1(const Problem& pb, const void* h, const void* dz, const void* beta, void* ddz,
+                              float* partial, uint32_t* blocks);
+// Multi-event weight gradient partials: [P][E][S][C].
+cudaError_t launch_wgrad(const Problem& pb, const void* carrier, const void* const* z, float* partial,
+                         uint32_t* blocks);
+// out[(row / S) * C * S + c * S + row % S] = sum_p partial[(p * rows + row) * C + c]
+cudaError_t launch_finish(const float* partial, float* out, uint32_t blocks, uint32_t rows, uint32_t C,
+                          uint32_t S, cudaStream_t stream);
+cudaError_t launch_tri_fwd(const Problem& pb, const void* base, const void* const* dz, const void* gamma, void* out);
+// Partials [P][J][C]; ddz may be null.
+cudaError_t launch_tri_bwd(const Problem& pb, const void* grad, const void* const* dz, const void* gamma,
+                           void* const* ddz, float* partial, uint32_t* blocks);
+
+// ---- shared launch plumbing -------------------------------------------------------------------
+struct BlockShape { uint32_t cl, tl, gy, threads; };
+
+inline BlockShape block_shape(uint32_t ncv, int target_threads) {
+    BlockShape b;
+    const uint32_t target = static_cast<uint32_t>(target_threads);
+    if (ncv <= static_cast<uint32_t>(kMaxThreads)) { b.cl = ncv; b.gy = 1; }
+    else { b.cl = 256; b.gy = (ncv + 255) / 256; }
+    uint32_t tl = (target + b.cl / 2) / b.cl;
+    if (tl < 1) tl = 1;
+    while (tl > 1 && tl * b.cl > static_cast<uint32_t>(kMaxThreads)) --tl;
+    b.tl = tl;
+    b.threads = b.cl * b.tl;
+    return b;
+}
+
+template <typename K>
+inline int occupancy_blocks(K kernel, int threads) {
+    static int cache[kMaxThreads + 1];   // one table per kernel instantiation; 0 = unknown
+    int v = cache[threads];
+    if (v == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, kernel, threads, 0) != cudaSuccess || v < 1) v = 1;
+        cache[threads] = v;
+    }
+    return v;
+}
+
+}  // namespace sihc

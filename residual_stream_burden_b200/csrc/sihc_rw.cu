@@ -1,0 +1,388 @@
+// SiHC read / write streaming kernels (forward, and the fused single-event adjoints).
+//
+// All four kernels are HBM-bound diagonal maps: per workspace token and channel
+// they touch S carrier elements and a handful of workspace elements, with at
+// most 2*S FMAs.  The design goal is therefore bytes in flight, not math:
+// every thread issues TT*(S+1) independent 16-byte loads before its first use,
+// coefficient vectors live in registers (single event) or come from L1 in the
+// native [E,C,S] layout (stage ops), and results leave as 16-byte streaming stores.
+//
+// Algorithmic traffic per (token, channel) element, in elements:
+//   read  fwd : S + E          write fwd : 2S + E (S + E without the carry)
+//   read  bwd (E = 1, fused dX + dalpha) : 2S + 1
+//   write bwd (E = 1, fused ddz + dbeta) : S + 2
+#include "sihc_dispatch.cuh"
+
+namespace sihc {
+
+struct ReadFwdParams { const void* x; const void* w; MutPtrs out; int E; Tiling t; };
+struct WriteFwdParams { const void* x; ConstPtrs dz; const void* w; void* y; int E; Tiling t; };
+struct ReadBwd1Params { const void* x; const void* g; const void* w; void* dx; float* partial; Tiling t; };
+struct WriteBwd1Params { const void* h; const void* dz; const void* w; void* ddz; float* partial; Tiling t; };
+
+
+// ---- stage read, forward ---------------------------------------------------------------------
+// out[l][m,c] = sum_s alpha[l,c,s] * X[m,s,c]
+// (reference: `_read`, sihc/models/sihc/sublayer_kernels.py:28-49; E = 1: `read_torch`,
+//  sihc/bench/fusion_controls.py:14-20)
+template <typename T, typename W, int S, int V, int TT, bool SINGLE>
+__global__ void __launch_bounds__(kMaxThreads) read_fwd_kernel(const __grid_constant__ ReadFwdParams p) {
+    typedef VecIO<T, V> IO;
+    typedef typename IO::Raw Raw;
+    const Tiling& t = p.t;
+    const Lane ln = make_lane<V>(t);
+    if (!ln.active) return;
+    const T* __restrict__ x = static_cast<const T*>(p.x) + ln.c0;
+    const W* __restrict__ wt = static_cast<const W*>(p.w) + static_cast<size_t>(ln.c0) * S;
+    float w1[S][V];
+    if constexpr (SINGLE) load_coeffs<W, S, V>(wt, w1);
+    const uint32_t per_tile = t.tl * TT;
+
+    for (uint32_t tile = blockIdx.x; tile < t.ntiles; tile += gridDim.x) {
+        Raw xr[TT][S];
+        uint32_t m[TT];
+#pragma unroll
+        for (int i = 0; i < TT; ++i) {
+            m[i] = tile * per_tile + i * t.tl + ln.tl;
+            const bool ok = m[i] < t.M;
+            const T* cell = x + cell_origin<S>(ok ? m[i] : 0u, t.g, t.C);
+#pragma unroll
+            for (int s = 0; s < S; ++s) xr[i][s] = ok ? IO::load_raw(cell + slot_offset<S>(s, t.g, t.C)) : IO::zero_raw();
+        }
+        if constexpr (SINGLE) {
+            T* __restrict__ out = static_cast<T*>(p.out.p[0]) + ln.c0;
+#pragma unroll
+            for (int i = 0; i < TT; ++i) {
+                float acc[V];
+#pragma unroll
+                for (int s = 0; s < S; ++s) {
+                    float xv[V];
+                    IO::unpack(xr[i][s], xv);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) acc[v] = s == 0 ? xv[v] * w1[0][v] : fmaf(xv[v], w1[s][v], acc[v]);
+                }
+                if (m[i] < t.M) IO::store(out + static_cast<size_t>(m[i]) * t.C, acc);
+            }
+        } else {
+#pragma unroll 1
+            for (int l = 0; l < p.E; ++l) {
+                if (p.out.p[l] == nullptr) continue;      // output not wanted
+                float w[S][V];
+                load_coeffs<W, S, V>(wt + static_cast<size_t>(l) * t.C * S, w);
+                T* __restrict__ out = static_cast<T*>(p.out.p[l]) + ln.c0;
+#pragma unroll
+                for (int i = 0; i < TT; ++i) {
+                    float acc[V];
+#pragma unroll
+                    for (int s = 0; s < S; ++s) {
+                        float xv[V];
+                        IO::unpack(xr[i][s], xv);
+#pragma unroll
+                        for (int v = 0; v < V; ++v) acc[v] = s == 0 ? xv[v] * w[0][v] : fmaf(xv[v], w[s][v], acc[v]);
+                    }
+                    if (m[i] < t.M) IO::store(out + static_cast<size_t>(m[i]) * t.C, acc);
+                }
+            }
+        }
+    }
+}
+
+// ---- stage write, forward ----------------------------------------------------------------------
+// y[m,s,c] = (x ? x[m,s,c] : 0) + sum_l beta[l,c,s] * dz[l][m,c]
+// (reference: `_write`, sihc/models/sihc/sublayer_kernels.py:82-97; a null dz[l] is skipped,
+//  which is how the read's carrier gradient treats unused read outputs)
+template <typename T, typename W, int S, int V, int TT, bool SINGLE>
+__global__ void __launch_bounds__(kMaxThreads) write_fwd_kernel(const __grid_constant__ WriteFwdParams p) {
+    typedef VecIO<T, V> IO;
+    typedef typename IO::Raw Raw;
+    const Tiling& t = p.t;
+    const Lane ln = make_lane<V>(t);
+    if (!ln.active) return;
+    const T* __restrict__ x = p.x ? static_cast<const T*>(p.x) + ln.c0 : nullptr;
+    T* __restrict__ y = static_cast<T*>(p.y) + ln.c0;
+    const W* __restrict__ wt = static_cast<const W*>(p.w) + static_cast<size_t>(ln.c0) * S;
+    float w1[S][V];
+    if constexpr (SINGLE) load_coeffs<W, S, V>(wt, w1);
+    const uint32_t per_tile = t.tl * TT;
+
+    for (uint32_t tile = blockIdx.x; tile < t.ntiles; tile += gridDim.x) {
+        uint32_t m[TT];
+        size_t origin[TT];
+        if constexpr (SINGLE) {
+            Raw xr[TT][S];
+            Raw dr[TT];
+            const T* __restrict__ dz = static_cast<const T*>(p.dz.p[0]) + ln.c0;
+#pragma unroll
+            for (int i = 0; i < TT; ++i) {
+                m[i] = tile * per_tile + i * t.tl + ln.tl;
+                const bool ok = m[i] < t.M;
+                origin[i] = cell_origin<S>(ok ? m[i] : 0u, t.g, t.C);
+                dr[i] = ok ? IO::load_raw(dz + static_cast<size_t>(m[i]) * t.C) : IO::zero_raw();
+#pragma unroll
+                for (int s = 0; s < S; ++s)
+                    xr[i][s] = (ok && x != nullptr) ? IO::load_raw(x + origin[i] + slot_offset<S>(s, t.g, t.C)) : IO::zero_raw();
+            }
+#pragma unroll
+            for (int i = 0; i < TT; ++i) {
+                float d[V];
+                IO::unpack(dr[i], d);
+#pragma unroll
+                for (int s = 0; s < S; ++s) {
+                    float r[V];
+                    IO::unpack(xr[i][s], r);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) r[v] = fmaf(w1[s][v], d[v], r[v]);
+                    if (m[i] < t.M) IO::store(y + origin[i] + slot_offset<S>(s, t.g, t.C), r);
+                }
+            }
+        } else {
+            float acc[TT][S][V];
+#pragma unroll
+            for (int i = 0; i < TT; ++i) {
+                m[i] = tile * per_tile + i * t.tl + ln.tl;
+                const bool ok = m[i] < t.M;
+                origin[i] = cell_origin<S>(ok ? m[i] : 0u, t.g, t.C);
+#pragma unroll
+                for (int s = 0; s < S; ++s) {
+                    if (ok && x != nullptr) IO::load(x + origin[i] + slot_offset<S>(s, t.g, t.C), acc[i][s]);
+                    else {
+#pragma unroll
+                        for (int v = 0; v < V; ++v) acc[i][s][v] = 0.f;
+                    }
+                }
+            }
+#pragma unroll 1
+            for (int l = 0; l < p.E; ++l) {
+                if (p.dz.p[l] == nullptr) continue;
+                const T* __restrict__ dz = static_cast<const T*>(p.dz.p[l]) + ln.c0;
+                Raw dr[TT];
+#pragma unroll
+                for (int i = 0; i < TT; ++i)
+                    dr[i] = m[i] < t.M ? IO::load_raw(dz + static_cast<size_t>(m[i]) * t.C) : IO::zero_raw();
+                float w[S][V];
+                load_coeffs<W, S, V>(wt + static_cast<size_t>(l) * t.C * S, w);
+#pragma unroll
+                for (int i = 0; i < TT; ++i) {
+                    float d[V];
+                    IO::unpack(dr[i], d);
+#pragma unroll
+                    for (int s = 0; s < S; ++s)
+#pragma unroll
+                        for (int v = 0; v < V; ++v) acc[i][s][v] = fmaf(w[s][v], d[v], acc[i][s][v]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < TT; ++i) {
+                if (m[i] < t.M) {
+#pragma unroll
+                    for (int s = 0; s < S; ++s) IO::store(y + origin[i] + slot_offset<S>(s, t.g, t.C), acc[i][s]);
+                }
+            }
+        }
+    }
+}
+
+// ---- single-event read, backward (fused) ---------------------------------------------------
+// dx[m,s,c] = alpha[c,s] * g[m,c];  partial[block][s][c] = sum_{m in block} X[m,s,c] * g[m,c]
+// One pass over X and g produces both adjoints (the reference makes two passes:
+// `_write_impl(add_x=False)` and `_weights_backward`, sihc/models/sihc/sublayer_kernels.py:284).
+template <typename T, typename W, int S, int V, int TT>
+__global__ void __launch_bounds__(kMaxThreads) read_bwd1_kernel(const __grid_constant__ ReadBwd1Params p) {
+    typedef VecIO<T, V> IO;
+    typedef typename IO::Raw Raw;
+    __shared__ float red[kMaxThreads * V];
+    const Tiling& t = p.t;
+    const Lane ln = make_lane<V>(t);
+    const T* __restrict__ x = static_cast<const T*>(p.x) + ln.c0;
+    const T* __restrict__ g = static_cast<const T*>(p.g) + ln.c0;
+    T* __restrict__ dx = p.dx ? static_cast<T*>(p.dx) + ln.c0 : nullptr;
+    const bool want_w = p.partial != nullptr;
+    float w1[S][V];
+    float acc[S][V];
+#pragma unroll
+    for (int s = 0; s < S; ++s)
+#pragma unroll
+        for (int v = 0; v < V; ++v) { acc[s][v] = 0.f; w1[s][v] = 0.f; }
+    if (ln.active) {
+        load_coeffs<W, S, V>(static_cast<const W*>(p.w) + static_cast<size_t>(ln.c0) * S, w1);
+        const uint32_t per_tile = t.tl * TT;
+        for (uint32_t tile = blockIdx.x; tile < t.ntiles; tile += gridDim.x) {
+            Raw xr[TT][S];
+            Raw gr[TT];
+            uint32_t m[TT];
+            size_t origin[TT];
+#pragma unroll
+            for (int i = 0; i < TT; ++i) {
+                m[i] = tile * per_tile + i * t.tl + ln.tl;
+                const bool ok = m[i] < t.M;
+                origin[i] = cell_origin<S>(ok ? m[i] : 0u, t.g, t.C);
+                gr[i] = ok ? IO::load_raw(g + static_cast<size_t>(m[i]) * t.C) : IO::zero_raw();
+#pragma unroll
+                for (int s = 0; s < S; ++s)
+                    xr[i][s] = (ok && want_w) ? IO::load_raw(x + origin[i] + slot_offset<S>(s, t.g, t.C)) : IO::zero_raw();
+            }
+#pragma unroll
+            for (int i = 0; i < TT; ++i) {
+                float gv[V];
+                IO::unpack(gr[i], gv);
+#pragma unroll
+                for (int s = 0; s < S; ++s) {
+                    float xv[V];
+                    float d[V];
+                    IO::unpack(xr[i][s], xv);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        d[v] = w1[s][v] * gv[v];
+                        acc[s][v] = fmaf(xv[v], gv[v], acc[s][v]);
+                    }
+                    if (dx != nullptr && m[i] < t.M) IO::store(dx + origin[i] + slot_offset<S>(s, t.g, t.C), d);
+                }
+            }
+        }
+    }
+    if (want_w)
+        block_reduce_rows<S, V>(acc, p.partial + static_cast<size_t>(blockIdx.x) * S * t.C, t.C, ln.c0, ln.cl, ln.tl,
+                                t.cl, t.tl, ln.active, red);
+}
+
+// ---- single-event write, backward (fused) --------------------------------------------------
+// ddz[m,c] = sum_s beta[c,s] * h[m,s,c];  partial[block][s][c] = sum_{m in block} dz[m,c] * h[m,s,c]
+// (reference: `sublayer_read(grad, beta)` + `_weights_backward(grad, updates, beta)`,
+//  sihc/models/sihc/sublayer_kernels.py:300-303)
+template <typename T, typename W, int S, int V, int TT>
+__global__ void __launch_bounds__(kMaxThreads) write_bwd1_kernel(const __grid_constant__ WriteBwd1Params p) {
+    typedef VecIO<T, V> IO;
+    typedef typename IO::Raw Raw;
+    __shared__ float red[kMaxThreads * V];
+    const Tiling& t = p.t;
+    const Lane ln = make_lane<V>(t);
+    const T* __restrict__ h = static_cast<const T*>(p.h) + ln.c0;
+    const T* __restrict__ dz = p.dz ? static_cast<const T*>(p.dz) + ln.c0 : nullptr;
+    T* __restrict__ ddz = p.ddz ? static_cast<T*>(p.ddz) + ln.c0 : nullptr;
+    const bool want_w = p.partial != nullptr && dz != nullptr;
+    float w1[S][V];
+    float acc[S][V];
+#pragma unroll
+    for (int s = 0; s < S; ++s)
+#pragma unroll
+        for (int v = 0; v < V; ++v) { acc[s][v] = 0.f; w1[s][v] = 0.f; }
+    if (ln.active) {
+        load_coeffs<W, S, V>(static_cast<const W*>(p.w) + static_cast<size_t>(ln.c0) * S, w1);
+        const uint32_t per_tile = t.tl * TT;
+        for (uint32_t tile = blockIdx.x; tile < t.ntiles; tile += gridDim.x) {
+            Raw hr[TT][S];
+            Raw dr[TT];
+            uint32_t m[TT];
+#pragma unroll
+            for (int i = 0; i < TT; ++i) {
+                m[i] = tile * per_tile + i * t.tl + ln.tl;
+                const bool ok = m[i] < t.M;
+                const T* cell = h + cell_origin<S>(ok ? m[i] : 0u, t.g, t.C);
+                dr[i] = (ok && want_w) ? IO::load_raw(dz + static_cast<size_t>(m[i]) * t.C) : IO::zero_raw();
+#pragma unroll
+                for (int s = 0; s < S; ++s) hr[i][s] = ok ? IO::load_raw(cell + slot_offset<S>(s, t.g, t.C)) : IO::zero_raw();
+            }
+#pragma unroll
+            for (int i = 0; i < TT; ++i) {
+                float dv[V];
+                float z[V];
+                IO::unpack(dr[i], dv);
+#pragma unroll
+                for (int s = 0; s < S; ++s) {
+                    float hv[V];
+                    IO::unpack(hr[i][s], hv);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        z[v] = s == 0 ? hv[v] * w1[0][v] : fmaf(hv[v], w1[s][v], z[v]);
+                        acc[s][v] = fmaf(hv[v], dv[v], acc[s][v]);
+                    }
+                }
+                if (ddz != nullptr && m[i] < t.M) IO::store(ddz + static_cast<size_t>(m[i]) * t.C, z);
+            }
+        }
+    }
+    if (p.partial != nullptr)
+        block_reduce_rows<S, V>(acc, p.partial + static_cast<size_t>(blockIdx.x) * S * t.C, t.C, ln.c0, ln.cl, ln.tl,
+                                t.cl, t.tl, ln.active, red);
+}
+
+// ---- host launchers ------------------------------------------------------------------------------
+namespace {
+constexpr int kFwdThreads = 384;
+constexpr int kBwdThreads = 384;
+constexpr int kFwdTT = 2;
+constexpr int kBwdTT = 2;
+inline int pick_tt(int dflt) { return tuning().tt > 0 ? tuning().tt : dflt; }
+}  // namespace
+
+cudaError_t launch_read_fwd(const Problem& pb, const void* x, const void* alpha, void* const* out) {
+    ReadFwdParams p{};
+    p.x = x; p.w = alpha; p.E = pb.E;
+    for (int l = 0; l < pb.E; ++l) p.out.p[l] = out[l];
+    return dispatch_types(pb.dtype, pb.wdtype, [&](auto tt_, auto ww_) {
+        using T = decltype(tt_); using W = decltype(ww_);
+        return dispatch_slots(pb.S, [&](auto s_) {
+            constexpr int S = decltype(s_)::value;
+            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kFwdTT), [&](auto v_, auto t_) {
+                constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
+                if (pb.E == 1)
+                    return launch_persistent(read_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kFwdThreads, 1, false, nullptr);
+                return launch_persistent(read_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, kFwdThreads, 1, false, nullptr);
+            });
+        });
+    });
+}
+
+cudaError_t launch_write_fwd(const Problem& pb, const void* x, const void* const* dz, const void* beta, void* y) {
+    WriteFwdParams p{};
+    p.x = x; p.w = beta; p.y = y; p.E = pb.E;
+    for (int l = 0; l < pb.E; ++l) p.dz.p[l] = dz[l];
+    return dispatch_types(pb.dtype, pb.wdtype, [&](auto tt_, auto ww_) {
+        using T = decltype(tt_); using W = decltype(ww_);
+        return dispatch_slots(pb.S, [&](auto s_) {
+            constexpr int S = decltype(s_)::value;
+            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kFwdTT), [&](auto v_, auto t_) {
+                constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
+                if (pb.E == 1 && dz[0] != nullptr)
+                    return launch_persistent(write_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kFwdThreads, 1, false, nullptr);
+                return launch_persistent(write_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, kFwdThreads, 1, false, nullptr);
+            });
+        });
+    });
+}
+
+cudaError_t launch_read_bwd1(const Problem& pb, const void* x, const void* g, const void* alpha, void* dx,
+                             float* partial, uint32_t* blocks) {
+    ReadBwd1Params p{};
+    p.x = x; p.g = g; p.w = alpha; p.dx = dx; p.partial = partial;
+    return dispatch_types(pb.dtype, pb.wdtype, [&](auto tt_, auto ww_) {
+        using T = decltype(tt_); using W = decltype(ww_);
+        return dispatch_slots(pb.S, [&](auto s_) {
+            constexpr int S = decltype(s_)::value;
+            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kBwdTT), [&](auto v_, auto t_) {
+                constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
+                return launch_persistent(read_bwd1_kernel<T, W, S, V, TT>, p, pb, V, TT, kBwdThreads, 1,
+                                         partial != nullptr, blocks);
+            });
+        });
+    });
+}
+
+cudaError_t launch_write_bwd1(const Problem& pb, const void* h, const void* dz, const void* beta, void* ddz,
+                              float* partial, uint32_t* blocks) {
+    WriteBwd1Params p{};
+    p.h = h; p.dz = dz; p.w = beta; p.ddz = ddz; p.partial = partial;
+    return dispatch_types(pb.dtype, pb.wdtype, [&](auto tt_, auto ww_) {
+        using T = decltype(tt_); using W = decltype(ww_);
+        return dispatch_slots(pb.S, [&](auto s_) {
+            constexpr int S = decltype(s_)::value;
+            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kBwdTT), [&](auto v_, auto t_) {
+                constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
+                return launch_persistent(write_bwd1_kernel<T, W, S, V, TT>, p, pb, V, TT, kBwdThreads, 1,
+                                         partial != nullptr, blocks);
+            });
+        });
+    });
+}
+
+}  // namespace sihc

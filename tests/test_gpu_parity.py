@@ -1,0 +1,312 @@
+"""CUDA kernels vs the CPU oracle and the reference-generated golden fixtures.
+
+Everything here goes through the C ABI (ctypes) of the in-tree library, either
+directly or via the ``sihc_b200::*`` operators.  Tolerances:
+  * fp32: relative L2 <= 1e-5 and elementwise atol = rtol = 2e-4 (the reference's
+    own bound, research/tests/test_sublayer_kernels.py:33-36);
+  * bf16 storage with fp32 accumulation: relative L2 <= 2e-2 and elementwise
+    atol 0.025 / rtol 0.03.
+"""
+
+import pytest
+import torch
+
+from conftest import load_golden, regenerate_op_inputs
+from oracle import sihc_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def R():
+    import residual_stream_burden_b200 as pkg
+    return pkg
+
+
+def close(actual, expected, dtype, what=""):
+    a, e = actual.detach().float().cpu(), expected.detach().float().cpu()
+    assert a.shape == e.shape, (what, a.shape, e.shape)
+    rel = (a - e).norm() / e.norm().clamp_min(1e-12)
+    assert rel <= (1e-5 if dtype == torch.float32 else 2e-2), (what, float(rel))
+    atol, rtol = (2e-4, 2e-4) if dtype == torch.float32 else (0.025, 0.03)
+    torch.testing.assert_close(a, e, atol=atol, rtol=rtol, msg=lambda m: f"{what}: {m}")
+
+
+def run_all(R, x, alpha, beta, dz, gz, gy):
+    """Forward and every gradient of the stage read and write through the public ops."""
+    xd, ad, bd = (t.to(DEV).requires_grad_() for t in (x, alpha, beta))
+    dzd = [t.to(DEV).requires_grad_() for t in dz]
+    z = R.sublayer_read(xd, ad)
+    dx_read, dalpha = torch.autograd.grad(z, (xd, ad), [t.to(DEV) for t in gz])
+    y = R.sublayer_write(xd, dzd, bd)
+    dx_write, dbeta, *ddz = torch.autograd.grad(y, (xd, bd, *dzd), gy.to(DEV))
+    return dict(z=torch.stack(z), y=y, dx_read=dx_read, dalpha=dalpha, dx_write=dx_write, dbeta=dbeta,
+                ddz=torch.stack(ddz))
+
+
+@pytest.mark.parametrize("tag", ["fp32", "bf16"])
+@pytest.mark.parametrize("case", ["tails_s4_e24", "tails_s16_e16", "vec_s4_e8"])
+def test_golden_op_cases(R, case, tag):
+    meta, t = load_golden(f"{case}_{tag}")
+    dtype = getattr(torch, meta["dtype"])
+    got = run_all(R, t["x"], t["alpha"], t["beta"], list(t["dz"].unbind(0)), list(t["gz"].unbind(0)), t["gy"])
+    for key in ("z", "y", "dx_read", "dalpha", "dx_write", "dbeta", "ddz"):
+        close(got[key], t[key], dtype, f"{case}_{tag}:{key}")
+    assert torch.equal(got["dx_write"].cpu(), t["gy"])
+
+
+@pytest.mark.parametrize("tag", ["fp32", "bf16"])
+def test_golden_config1_seed0(R, tag):
+    """BASELINE config 1: batch 4, 256 tokens, n=4, width 768, seed 0, all outputs and gradients."""
+    meta, t = load_golden(f"cfg1_{tag}")
+    dtype = getattr(torch, meta["dtype"])
+    stride = meta["sample_stride"]
+    inp = regenerate_op_inputs(meta)
+    assert torch.equal(inp["x"].flatten()[::stride], t["x_sample"])
+    # single-event public API (autograd.Function path)
+    xd = inp["x"].to(DEV).requires_grad_()
+    ad = inp["alpha"][0].to(DEV).requires_grad_()
+    bd = inp["beta"][0].to(DEV).requires_grad_()
+    dzd = inp["dz"][0].to(DEV).requires_grad_()
+    z = R.sihc_read(xd, ad)
+    dx_read, dalpha = torch.autograd.grad(z, (xd, ad), inp["gz"][0].to(DEV))
+    y = R.sihc_write(xd, dzd, bd)
+    dx_write, dbeta, ddz = torch.autograd.grad(y, (xd, bd, dzd), inp["gy"].to(DEV))
+    got = dict(z=z, y=y, dx_read=dx_read, dalpha=dalpha, dx_write=dx_write, dbeta=dbeta, ddz=ddz)
+    for key, val in got.items():
+        close(val.flatten()[::stride], t[key], dtype, f"cfg1_{tag}:{key}")
+    # and the whole tensors against the oracle
+    close(z, O.read(inp["x"], inp["alpha"][0]), dtype, "z full")
+    close(y, O.write(inp["x"], [inp["dz"][0]], inp["beta"]), dtype, "y full")
+    odx, oda = O.read_backward(inp["x"], [inp["gz"][0]], inp["alpha"], acc=torch.float64)
+    oddz, odb = O.write_backward(inp["gy"], [inp["dz"][0]], inp["beta"], acc=torch.float64)
+    close(dx_read, odx, dtype, "dx full")
+    close(ddz, oddz[0], dtype, "ddz full")
+    close(dalpha, oda[0].to(dtype), dtype, "dalpha full")
+    close(dbeta, odb[0].to(dtype), dtype, "dbeta full")
+
+
+@pytest.mark.parametrize("tag", ["fp32", "bf16"])
+@pytest.mark.parametrize("case", ["tri_a3", "tri_a23"])
+def test_golden_triangular(R, case, tag):
+    meta, t = load_golden(f"{case}_{tag}")
+    dtype = getattr(torch, meta["dtype"])
+    base = t["base"].to(DEV).requires_grad_()
+    ups = [u.to(DEV).requires_grad_() for u in t["updates"].unbind(0)]
+    gamma = t["gamma"].to(DEV).requires_grad_()
+    out = R.sublayer_triangular(base, ups, gamma)
+    dbase, dgamma, *ddz = torch.autograd.grad(out, (base, gamma, *ups), t["grad"].to(DEV))
+    close(out, t["out"], dtype, "out")
+    assert torch.equal(out.cpu(), t["out"])           # same fp32 order as the reference: bit-exact
+    close(torch.stack(ddz), t["ddz"], dtype, "ddz")
+    close(dgamma, t["dgamma"], t["gamma"].dtype, "dgamma")
+    assert torch.equal(dbase.cpu(), t["grad"])
+
+
+CASES = [
+    # slots, batch, grid, channels, events, dtype, weights fp32?
+    (2, 2, 5, 64, 1, torch.bfloat16, False),
+    (2, 3, 3, 37, 3, torch.float32, False),
+    (4, 2, 16, 768, 1, torch.bfloat16, True),
+    (4, 5, 9, 1152, 2, torch.bfloat16, False),
+    (4, 3, 7, 67, 24, torch.bfloat16, False),
+    (4, 1, 16, 100, 12, torch.float32, False),
+    (8, 2, 6, 128, 1, torch.bfloat16, False),
+    (8, 2, 5, 36, 5, torch.float32, False),
+    (16, 2, 4, 64, 1, torch.bfloat16, False),
+    (16, 3, 11, 67, 16, torch.bfloat16, True),
+    (16, 1, 16, 256, 8, torch.float32, False),
+    (4, 9, 16, 768, 16, torch.bfloat16, False),
+]
+
+
+@pytest.mark.parametrize("slots,b,g,c,events,dtype,wf32", CASES)
+def test_random_shapes_vs_oracle(R, slots, b, g, c, events, dtype, wf32):
+    torch.manual_seed(1000 + slots * 37 + c + events)
+    kh, kw = O.cell_shape(slots)
+    wdtype = torch.float32 if wf32 else dtype
+    x = torch.randn(b, g * kh, g * kw, c).to(dtype)
+    alpha = (1.0 / slots + 0.05 * torch.randn(events, c, slots)).to(wdtype)
+    beta = (1.0 + 0.05 * torch.randn(events, c, slots)).to(wdtype)
+    dz = [torch.randn(b, g * g, c).to(dtype) for _ in range(events)]
+    gz = [torch.randn(b, g * g, c).to(dtype) for _ in range(events)]
+    gy = torch.randn(b, g * kh, g * kw, c).to(dtype)
+    got = run_all(R, x, alpha, beta, dz, gz, gy)
+    close(got["z"], torch.stack(O.multi_read(x, alpha)), dtype, "z")
+    close(got["y"], O.write(x, dz, beta), dtype, "y")
+    odx, oda = O.read_backward(x, gz, alpha, acc=torch.float64)
+    oddz, odb = O.write_backward(gy, dz, beta, acc=torch.float64)
+    close(got["dx_read"], odx, dtype, "dx_read")
+    close(got["ddz"], torch.stack(oddz), dtype, "ddz")
+    close(got["dalpha"], oda.to(wdtype), wdtype, "dalpha")
+    close(got["dbeta"], odb.to(wdtype), wdtype, "dbeta")
+    assert got["dalpha"].dtype == wdtype and got["dbeta"].dtype == wdtype
+
+
+def test_packed_layout_contract_and_unused_reads(R):
+    # research/tests/test_sublayer_kernels.py:111-123
+    x = torch.randn(1, 16, 16, 37, device=DEV, requires_grad=True)
+    a = torch.randn(16, 37, 16, device=DEV, requires_grad=True)
+    with pytest.raises(ValueError, match="contiguous|packed"):
+        R.sublayer_read(x.transpose(1, 2), a)
+    base = R.sublayer_read(x, a)
+    padded = torch.randn(2, 18, 37, device=DEV)
+    bad = padded[:, 2:]
+    with pytest.raises(ValueError, match="contiguous|packed"):
+        R.sublayer_triangular(bad, [bad], torch.ones(1, 37, device=DEV))
+    base[0].sum().backward()
+    assert torch.count_nonzero(a.grad[1:]) == 0
+    assert torch.count_nonzero(a.grad[0]) > 0
+    xo, ao = x.detach().cpu(), a.detach().cpu()
+    odx, oda = O.read_backward(xo, [torch.ones(1, 16, 37)] + [None] * 15, ao)
+    close(x.grad, odx, torch.float32, "dx with unused outputs")
+    close(a.grad, oda, torch.float32, "dalpha with unused outputs")
+
+
+def test_error_contract(R):
+    x = torch.randn(2, 8, 8, 16, device=DEV)
+    a = torch.randn(4, 16, 4, device=DEV)
+    with pytest.raises(ValueError):
+        R.sublayer_read(x, a[:, :8].contiguous())                      # channel mismatch
+    with pytest.raises(ValueError):
+        R.sublayer_read(x, torch.randn(4, 16, 3, device=DEV))          # unsupported slot count
+    with pytest.raises(ValueError):
+        R.sublayer_read(x, torch.randn(25, 16, 4, device=DEV))         # too many events
+    with pytest.raises(ValueError):
+        R.sublayer_read(x.half(), a.half())                            # unsupported dtype
+    with pytest.raises(ValueError):
+        R.sublayer_read(x.cpu(), a.cpu())                              # not CUDA: no CPU fallback
+    with pytest.raises(ValueError):
+        R.sublayer_write(x, [torch.randn(2, 16, 16, device=DEV)] * 3, a)   # one update per event
+    with pytest.raises(ValueError):
+        R.sublayer_write(x, [torch.randn(2, 15, 16, device=DEV)] * 4, a)   # wrong token count
+    with pytest.raises(ValueError):
+        R.sublayer_triangular(torch.randn(2, 16, 16, device=DEV), [], torch.ones(0, 16, device=DEV))
+    with pytest.raises(ValueError):
+        R.blockwise_read(x, a)                                         # block-wise needs 8 or 12 events
+
+
+def test_weight_gradients_are_deterministic(R):
+    torch.manual_seed(5)
+    x = torch.randn(8, 32, 32, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    a = (0.25 + 0.02 * torch.randn(1, 256, 4, device=DEV)).to(torch.bfloat16).requires_grad_()
+    g = torch.randn(8, 256, 256, device=DEV, dtype=torch.bfloat16)
+    runs = []
+    for _ in range(3):
+        z = R.sublayer_read(x, a)
+        runs.append(torch.autograd.grad(z, (x, a), [g]))
+    for dx, da in runs[1:]:
+        assert torch.equal(dx, runs[0][0]) and torch.equal(da, runs[0][1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("events,slots", [(16, 4), (24, 4), (8, 16)])
+def test_stage_recurrence_matches_literal_carrier(R, events, slots, dtype):
+    """read -> triangular -> write staged == literal dense recurrence, all gradients
+    (research/tests/test_sublayer_kernels.py:76-108; oracle in place of the CUDA einsum)."""
+    torch.manual_seed(92)
+    k = int(slots ** 0.5)
+    x = torch.randn(2, 4 * k, 4 * k, 37).to(dtype)
+    alpha = (torch.randn(events, 37, slots) * 0.07).to(dtype)
+    beta = (torch.randn(events, 37, slots) * 0.07).to(dtype)
+    xd, ad, bd = (t.to(DEV).requires_grad_() for t in (x, alpha, beta))
+    base = R.sublayer_read(xd, ad)
+    gamma = (ad[:, None] * bd[None, :]).sum(-1)
+    updates = []
+    for i in range(events):
+        z = base[i] if i == 0 else R.sublayer_triangular(base[i], updates, gamma[i, :i].contiguous())
+        updates.append((0.05 * z.tanh()).contiguous())
+    out = R.sublayer_write(xd, updates, bd)
+    xr, ar, br = (t.clone().requires_grad_() for t in (x, alpha, beta))
+    ref = O.literal_stage(xr, ar, br, [lambda z: 0.05 * z.tanh()] * events)
+    upstream = (torch.randn(out.shape) * 0.1).to(dtype)
+    ga = torch.autograd.grad(out, (xd, ad, bd), upstream.to(DEV))
+    gr = torch.autograd.grad(ref, (xr, ar, br), upstream)
+    atol, rtol = (2e-4, 2e-4) if dtype == torch.float32 else (0.025, 0.03)
+    torch.testing.assert_close(out.cpu(), ref, atol=atol, rtol=rtol)
+    for a, b in zip(ga, gr):
+        torch.testing.assert_close(a.cpu(), b, atol=atol, rtol=rtol)
+        rel = (a.cpu().float() - b.float()).norm() / b.float().norm().clamp_min(1e-8)
+        assert rel < (0.035 if dtype == torch.bfloat16 else 1e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("active", [1, 3, 8, 23, 24])
+def test_triangular_tails_and_mixed_gamma(R, dtype, active):
+    torch.manual_seed(583)
+    base = torch.randn(3, 49, 67).to(dtype)
+    ups = [torch.randn(3, 49, 67).to(dtype) for _ in range(active)]
+    gamma = torch.randn(active, 67) * 0.05                     # fp32 gamma with a bf16 workspace is allowed
+    grad = torch.randn(3, 49, 67).to(dtype)
+    bd = base.to(DEV).requires_grad_()
+    ud = [u.to(DEV).requires_grad_() for u in ups]
+    gd = gamma.to(DEV).requires_grad_()
+    out = R.sublayer_triangular(bd, ud, gd)
+    dbase, dgamma, *ddz = torch.autograd.grad(out, (bd, gd, *ud), grad.to(DEV))
+    assert torch.equal(out.cpu(), O.triangular(base, ups, gamma))
+    oddz, odg = O.triangular_backward(grad, ups, gamma, acc=torch.float64)
+    close(torch.stack(ddz), torch.stack(oddz), dtype, "ddz")
+    close(dgamma, odg.float(), torch.float32, "dgamma")
+    assert torch.equal(dbase.cpu(), grad)
+
+
+def test_large_size_properties(R):
+    """Size-independent properties at a size the oracle would take minutes on:
+    adjointness <read(x), g> == <x, read^T(g)>, linearity, and write(x, dz, 0*beta) == x."""
+    torch.manual_seed(11)
+    b, g, c, s = 512, 16, 768, 4                                 # M = 2^17 tokens, X = 805 MB in bf16
+    dtype = torch.bfloat16
+    x = torch.randn(b, 2 * g, 2 * g, c, device=DEV, dtype=dtype)
+    alpha = (0.25 + 0.02 * torch.randn(1, c, s, device=DEV)).to(dtype)
+    gz = torch.randn(b, g * g, c, device=DEV, dtype=dtype)
+    z = R.sublayer_read(x, alpha)[0]
+    dx, dalpha = R.ops._read_backward_op(x, [gz], alpha, True, True)
+    lhs = (z.double() * gz.double()).sum()
+    rhs = (x.double() * dx.double()).sum()
+    assert abs(lhs - rhs) / abs(lhs) < 5e-3                      # bf16 rounding of z and dx
+    # dalpha[c,s] = sum_m x*g  -> checks against a torch reduction on the GPU in fp64 chunks
+    cells = x.view(b * g, 2, g, 2, c)
+    ref = torch.zeros(c, s, dtype=torch.float64, device=DEV)
+    gv = gz.view(b * g, 1, g, 1, c)
+    for lo in range(0, b * g, 1024):
+        prod = cells[lo:lo + 1024].double() * gv[lo:lo + 1024].double()
+        ref += prod.sum((0, 2)).permute(2, 0, 1).reshape(c, s)
+    rel = (dalpha[0].double() - ref).norm() / ref.norm()
+    assert rel < 5e-3, float(rel)                                # result is rounded to bf16
+    zero_beta = torch.zeros(1, c, s, device=DEV, dtype=dtype)
+    y = R.sublayer_write(x, [gz], zero_beta)
+    assert torch.equal(y, x)
+    # linearity of the write in dz with beta = 1: write(x, dz, 1) - x == dz broadcast to every slot
+    ones = torch.ones(1, c, s, device=DEV, dtype=dtype)
+    y0 = R.ops._write_impl(x, [gz], ones, False)
+    assert torch.equal(y0.view(b * g, 2, g, 2, c), gz.view(b * g, 1, g, 1, c).expand(b * g, 2, g, 2, c))
+
+
+def test_c_abi_direct_calls_and_status_codes(R):
+    """Raw ctypes calls: status codes for bad arguments, no torch op layer in between."""
+    from residual_stream_burden_b200 import _lib
+    lib = _lib.lib
+    x = torch.randn(1, 4, 4, 8, device=DEV)
+    a = torch.full((1, 8, 4), 0.25, device=DEV)
+    out = torch.empty(1, 4, 8, device=DEV)
+    s = torch.cuda.current_stream().cuda_stream
+    args = (x.data_ptr(), a.data_ptr(), _lib.ptr_array([out.data_ptr()]), 1, 1, 2, 2, 2, 8)
+    assert lib.sihc_read_fwd(*args, _lib.F32, _lib.F32, s) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(out.cpu(), O.read(x.cpu(), a[0].cpu()), atol=1e-6)
+    assert lib.sihc_read_fwd(None, a.data_ptr(), _lib.ptr_array([out.data_ptr()]), 1, 1, 2, 2, 2, 8, 0, 0, s) == -1
+    assert lib.sihc_read_fwd(*args, 7, 0, s) == -2
+    assert lib.sihc_read_fwd(x.data_ptr(), a.data_ptr(), _lib.ptr_array([out.data_ptr()]), 0, 1, 2, 2, 2, 8, 0, 0, s) == -3
+    assert lib.sihc_read_fwd(x.data_ptr(), a.data_ptr(), _lib.ptr_array([out.data_ptr()]), 1, 1, 2, 3, 3, 8, 0, 0, s) == -4
+    assert lib.sihc_read_fwd(x.data_ptr(), a.data_ptr(), _lib.ptr_array([out.data_ptr()]), 1, 0, 2, 2, 2, 8, 0, 0, s) == -5
+    da = torch.empty(1, 8, 4, device=DEV)
+    dx = torch.empty_like(x)
+    assert lib.sihc_read_bwd(x.data_ptr(), _lib.ptr_array([out.data_ptr()]), a.data_ptr(), dx.data_ptr(), da.data_ptr(),
+                             None, 0, 1, 1, 2, 2, 2, 8, 0, 0, s) == -6
+    assert b"workspace" in lib.sihc_status_string(-6)
+    before = _lib.launch_count()
+    assert lib.sihc_read_fwd(*args, _lib.F32, _lib.F32, s) == 0
+    assert _lib.launch_count() == before + 1
+    torch.cuda.synchronize()

@@ -308,10 +308,11 @@ __global__ void __launch_bounds__(kMaxThreads) write_bwd1_kernel(const __grid_co
 
 // ---- host launchers ------------------------------------------------------------------------------
 namespace {
-constexpr int kFwdThreads = 384;
-constexpr int kBwdThreads = 384;
-constexpr int kFwdTT = 2;
-constexpr int kBwdTT = 2;
+// Defaults from a threads x tokens-per-thread sweep on B200 (n=4, width 768, 2^19 tokens, bf16).
+constexpr int kReadFwdThreads = 512, kReadFwdTT = 1;
+constexpr int kWriteFwdThreads = 384, kWriteFwdTT = 2;
+constexpr int kReadBwdThreads = 384, kReadBwdTT = 2;
+constexpr int kWriteBwdThreads = 512, kWriteBwdTT = 2;
 inline int pick_tt(int dflt) { return tuning().tt > 0 ? tuning().tt : dflt; }
 }  // namespace
 
@@ -323,11 +324,11 @@ cudaError_t launch_read_fwd(const Problem& pb, const void* x, const void* alpha,
         using T = decltype(tt_); using W = decltype(ww_);
         return dispatch_slots(pb.S, [&](auto s_) {
             constexpr int S = decltype(s_)::value;
-            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kFwdTT), [&](auto v_, auto t_) {
+            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(pb.E == 1 ? kReadFwdTT : 2), [&](auto v_, auto t_) {
                 constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
                 if (pb.E == 1)
-                    return launch_persistent(read_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kFwdThreads, 1, false, nullptr);
-                return launch_persistent(read_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, kFwdThreads, 1, false, nullptr);
+                    return launch_persistent(read_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kReadFwdThreads, 1, false, nullptr);
+                return launch_persistent(read_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, 384, 1, false, nullptr);
             });
         });
     });
@@ -341,11 +342,11 @@ cudaError_t launch_write_fwd(const Problem& pb, const void* x, const void* const
         using T = decltype(tt_); using W = decltype(ww_);
         return dispatch_slots(pb.S, [&](auto s_) {
             constexpr int S = decltype(s_)::value;
-            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kFwdTT), [&](auto v_, auto t_) {
+            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kWriteFwdTT), [&](auto v_, auto t_) {
                 constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
                 if (pb.E == 1 && dz[0] != nullptr)
-                    return launch_persistent(write_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kFwdThreads, 1, false, nullptr);
-                return launch_persistent(write_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, kFwdThreads, 1, false, nullptr);
+                    return launch_persistent(write_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kWriteFwdThreads, 1, false, nullptr);
+                return launch_persistent(write_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, kWriteFwdThreads, 1, false, nullptr);
             });
         });
     });
@@ -359,9 +360,9 @@ cudaError_t launch_read_bwd1(const Problem& pb, const void* x, const void* g, co
         using T = decltype(tt_); using W = decltype(ww_);
         return dispatch_slots(pb.S, [&](auto s_) {
             constexpr int S = decltype(s_)::value;
-            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kBwdTT), [&](auto v_, auto t_) {
+            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kReadBwdTT), [&](auto v_, auto t_) {
                 constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
-                return launch_persistent(read_bwd1_kernel<T, W, S, V, TT>, p, pb, V, TT, kBwdThreads, 1,
+                return launch_persistent(read_bwd1_kernel<T, W, S, V, TT>, p, pb, V, TT, kReadBwdThreads, 1,
                                          partial != nullptr, blocks);
             });
         });
@@ -376,9 +377,9 @@ cudaError_t launch_write_bwd1(const Problem& pb, const void* h, const void* dz, 
         using T = decltype(tt_); using W = decltype(ww_);
         return dispatch_slots(pb.S, [&](auto s_) {
             constexpr int S = decltype(s_)::value;
-            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kBwdTT), [&](auto v_, auto t_) {
+            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kWriteBwdTT), [&](auto v_, auto t_) {
                 constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
-                return launch_persistent(write_bwd1_kernel<T, W, S, V, TT>, p, pb, V, TT, kBwdThreads, 1,
+                return launch_persistent(write_bwd1_kernel<T, W, S, V, TT>, p, pb, V, TT, kWriteBwdThreads, 1,
                                          partial != nullptr, blocks);
             });
         });

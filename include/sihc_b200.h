@@ -106,6 +106,31 @@ int sihc_read_bwd(const void* x, const void* const* g, const void* alpha, void* 
                   int dtype, int wdtype, void* stream);
 
 /*
+ * sihc_read_bwd for callers that cannot allocate device memory.  No counterpart in
+ * the reference (its operators allocate their scratch with torch.zeros).
+ *
+ * Same inputs, outputs and results as sihc_read_bwd, but without the workspace
+ * arguments: the partial sums go to a fixed SIHC_STATIC_SCRATCH_BYTES array built
+ * into the library (held by every GPU that loads the library until the process
+ * exits).  Meant for hosts whose device memory is fully planned at start-up (fixed
+ * arenas, frozen memory maps) and for threads that must never trigger the implicit
+ * device synchronisation of cudaMalloc / cudaFree.  It calls no allocating routine.
+ *   - Returns SIHC_ERR_CAPACITY, before launching anything, when
+ *     sihc_wgrad_workspace_bytes(...) for the case exceeds SIHC_STATIC_SCRATCH_BYTES
+ *     (single event, 4 slots, 768 channels needs 3.6 MB; the limit is 16 MiB).
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call before
+ *     any stream capture.
+ *   - One array per device is shared by all calls: calls that can overlap on the GPU
+ *     race and must be serialised by the caller.  The array keeps the previous call's
+ *     partial sums; they are never read (every row is rewritten before use).
+ */
+#define SIHC_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
+int sihc_read_bwd_static(const void* x, const void* const* g, const void* alpha, void* dx, float* dalpha,
+                         int events, int64_t batch, int grid, int kh, int kw, int channels,
+                         int dtype, int wdtype, void* stream);
+
+/*
  * Stage write, backward w.r.t. the updates and beta (the carrier gradient of the
  * write is `h` itself and needs no kernel).
  *   ddz[l][m,c]     = sum_s beta[l,c,s] * h[m,s,c]

@@ -51,6 +51,10 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--workload", default="op", choices=["op", "sihc_b_fwd", "sihc_xl_train", "sihc_xl_sample"],
+                    help="op: the read/write path itself (headline); the others time the SiHC models around it")
+    ap.add_argument("--no-models", action="store_true", help="skip the model-level figures added to the op line")
+    ap.add_argument("--sample-steps", type=int, default=50)
     return ap.parse_args()
 
 
@@ -257,6 +261,105 @@ def run_e2e(args, batch, grid, slots, channels, dtype, device, steps):
     return seconds, h2d, d2h, chunk
 
 
+# ------------------------------------------------------------------------------------------ models
+def time_device(fn, steps, warmup, world, device):
+    """W untimed + K timed calls, CUDA events on the current stream, barrier on both sides, max over ranks."""
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = start.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps
+
+
+def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_steps=50):
+    """SiHC-B forward (batch 256), SiHC-XL training step (batch 32 per GPU, DDP) or SiHC-XL Heun sampling
+    (batch 256 per GPU, CFG 2.4 on [0.1, 0.9]); bf16 autocast over fp32 parameters, synthetic N(0,1) images,
+    random-init weights with opened gates.  Inputs start in pinned host memory every step."""
+    from residual_stream_burden_b200 import _lib
+    from residual_stream_burden_b200.model import sample_heun, sihc_b, sihc_xl, velocity_training_batch
+    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.backends.cudnn.allow_tf32 = True
+    torch.manual_seed(1234 + rank)
+    gen = torch.Generator().manual_seed(rank)
+    launches0 = _lib.launch_count()
+    if kind == "sihc_b_fwd":
+        batch = 256
+        model = sihc_b().to(device).eval()
+        model.open_gates()
+        x_host = torch.randn(batch, 3, 256, 256, generator=gen).pin_memory()
+        t = torch.rand(batch, device=device)
+        y = torch.randint(0, 1000, (batch,), device=device)
+
+        def step():
+            x = x_host.to(device, non_blocking=True)
+            with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                out = model(x, t, y)
+            return float(out.float().abs().mean())          # device -> host read of a scalar
+
+        ms = time_device(step, steps, warmup, world, device)
+        name = "SiHC-B forward, 12 blocks x 768, n=4, batch 256 per GPU, bf16 autocast"
+    elif kind == "sihc_xl_train":
+        batch = 32
+        model = sihc_xl().to(device)
+        model.open_gates()
+        net = model
+        if world > 1:
+            from torch.nn.parallel import DistributedDataParallel as DDP
+            net = DDP(model, device_ids=[local_rank], gradient_as_bucket_view=True)
+        opt = torch.optim.AdamW(model.parameters(), lr=2e-4, betas=(0.9, 0.95), weight_decay=0.0, fused=True)
+        x_host = torch.randn(batch, 3, 256, 256, generator=gen).pin_memory()
+        y = torch.randint(0, 1000, (batch,), device=device)
+
+        def step():
+            x = x_host.to(device, non_blocking=True)
+            z, t, v = velocity_training_batch(x)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                pred = net(z, t, y)
+            loss = (pred.float() - v).square().mean()
+            loss.backward()
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            return float(loss)                              # device -> host read of the loss
+
+        ms = time_device(step, steps, warmup, world, device)
+        name = "SiHC-XL training step, 28 blocks x 1152, n=4, stages 8+12+8, batch 32 per GPU, bf16 autocast + fp32 AdamW"
+    else:
+        batch = 256
+        model = sihc_xl().to(device).eval()
+        model.open_gates()
+        y = torch.randint(0, 1000, (batch,), device=device)
+
+        def step():
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                img = sample_heun(model, y, steps=sample_steps, cfg_scale=2.4, interval=(0.1, 0.9))
+            return float(img.float().abs().mean())
+
+        ms = time_device(step, steps, warmup, world, device)
+        name = f"SiHC-XL Heun sampling, {sample_steps} steps, CFG 2.4 on [0.1,0.9], batch 256 per GPU, bf16 autocast"
+    launches = _lib.launch_count() - launches0
+    res = {"workload": name, "img_per_s": round(world * batch / (ms * 1e-3), 2), "ms_per_step": round(ms, 3),
+           "global_batch": world * batch, "routing_launches_per_step": launches // max(1, steps + warmup),
+           "peak_mem_gb": round(torch.cuda.max_memory_allocated(device) / 2**30, 2)}
+    del model
+    torch.cuda.empty_cache()
+    return res
+
+
 # ------------------------------------------------------------------------------------------ CPU
 def cpu_step_factory(batch, grid, slots, channels, dtype):
     """The reference's unfused eager path on the host: read_torch/write_torch + autograd."""
@@ -332,6 +435,26 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     from residual_stream_burden_b200 import _lib
+
+    if args.workload != "op":
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        res = model_workload(args.workload, device, rank, world, local_rank, args.steps, max(args.warmup, 3),
+                             args.sample_steps)
+        clocks = sampler.stop() if rank == 0 else None
+        if rank == 0:
+            print(json.dumps({"metric": args.workload + "_throughput", "value": res["img_per_s"], "unit": "img/s",
+                              "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                              "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+                              "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                              "config": {"workload": res["workload"], "global_batch": res["global_batch"],
+                                         "parallelism": f"dp{world}"},
+                              "gpu_launches": res["routing_launches_per_step"] * args.steps,
+                              "peak_mem_gb": res["peak_mem_gb"], "clocks": clocks}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     inp = make_inputs(batch, grid, slots, channels, dtype, device, seed=rank)
     path = DevicePath(inp, batch, grid, slots, channels, dtype)
@@ -420,13 +543,22 @@ def main():
                "sample": f"{sample_batch} images ({sample_tokens} tokens) of the workload, torch eager on CPU, "
                          f"{sec * 1e3:.0f} ms per pass"}
 
+    models = None
+    if not args.no_models:
+        # second half of the headline metric: the models around the path, same process, same GPUs
+        del path, inp
+        torch.cuda.empty_cache()
+        models = {"sihc_xl_train": model_workload("sihc_xl_train", device, rank, world, local_rank, 5, 3)}
+        if world == 1:
+            models["sihc_b_fwd"] = model_workload("sihc_b_fwd", device, rank, world, local_rank, 5, 3)
+
     if rank == 0:
         line = {"metric": "sihc_read_write_fwd_bwd_bandwidth", "value": round(value, 1), "unit": "GB/s",
                 "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
                 "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "config": config,
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
-                "clocks": clocks}
+                "clocks": clocks, "models": models}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -226,21 +226,27 @@ __global__ void __launch_bounds__(kMaxThreads) tri_bwd_kernel(const __grid_const
                     for (int v = 0; v < V; ++v) gv[i][v] = 0.f;
                 }
             }
+            // issue every update load of the chunk before the first use (JC*TT vectors in flight)
+            typename VecIO<T, V>::Raw dr[JC][TT];
+#pragma unroll
+            for (int j = 0; j < JC; ++j) {
+                const int l = e0 + j;
+                const bool have = l < p.J && p.partial != nullptr;
+                const T* __restrict__ dz = have ? static_cast<const T*>(p.dz.p[l]) + ln.c0 : nullptr;
+#pragma unroll
+                for (int i = 0; i < TT; ++i)
+                    dr[j][i] = (have && ok[i]) ? VecIO<T, V>::load_raw(dz + off[i]) : VecIO<T, V>::zero_raw();
+            }
 #pragma unroll
             for (int j = 0; j < JC; ++j) {
                 const int l = e0 + j;
                 if (l < p.J) {
-                    if (p.partial != nullptr) {
-                        const T* __restrict__ dz = static_cast<const T*>(p.dz.p[l]) + ln.c0;
 #pragma unroll
-                        for (int i = 0; i < TT; ++i) {
-                            if (ok[i]) {
-                                float d[V];
-                                VecIO<T, V>::load(dz + off[i], d);
+                    for (int i = 0; i < TT; ++i) {
+                        float d[V];
+                        VecIO<T, V>::unpack(dr[j][i], d);
 #pragma unroll
-                                for (int v = 0; v < V; ++v) acc[j][v] = fmaf(gv[i][v], d[v], acc[j][v]);
-                            }
-                        }
+                        for (int v = 0; v < V; ++v) acc[j][v] = fmaf(gv[i][v], d[v], acc[j][v]);
                     }
                     if (p.has_ddz && p.ddz.p[l] != nullptr) {
                         T* __restrict__ ddz = static_cast<T*>(p.ddz.p[l]) + ln.c0;
@@ -329,10 +335,10 @@ cudaError_t launch_tri_fwd(const Problem& pb, const void* base, const void* cons
     for (int l = 0; l < pb.E; ++l) p.dz.p[l] = dz[l];
     return dispatch_types(pb.dtype, pb.wdtype, [&](auto tt_, auto ww_) {
         using T = decltype(tt_); using W = decltype(ww_);
-        return dispatch_tri_vec(pb.dtype, pb.V, pick_tt(kTT), [&](auto v_, auto t_) {
+        return dispatch_tri_vec(pb.dtype, pb.V, pick_tt(1), [&](auto v_, auto t_) {
             constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
             if constexpr (V > 16 / int(sizeof(T))) return cudaErrorInvalidValue;
-            else return launch_persistent(tri_fwd_kernel<T, W, V, TT>, p, pb, V, TT, kThreads, 1, false, nullptr);
+            else return launch_persistent(tri_fwd_kernel<T, W, V, TT>, p, pb, V, TT, 256, 1, false, nullptr);
         });
     });
 }
@@ -344,12 +350,12 @@ cudaError_t launch_tri_bwd(const Problem& pb, const void* grad, const void* cons
     for (int l = 0; l < pb.E; ++l) { p.dz.p[l] = dz[l]; p.ddz.p[l] = ddz ? ddz[l] : nullptr; }
     return dispatch_types(pb.dtype, pb.wdtype, [&](auto tt_, auto ww_) {
         using T = decltype(tt_); using W = decltype(ww_);
-        return dispatch_tri_vec(pb.dtype, pb.V, pick_tt(kTT), [&](auto v_, auto t_) {
+        return dispatch_tri_vec(pb.dtype, pb.V, pick_tt(1), [&](auto v_, auto t_) {
             constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
             if constexpr (V > 16 / int(sizeof(T))) return cudaErrorInvalidValue;
             else {
                 const uint32_t gz = static_cast<uint32_t>((pb.E + kTriChunk - 1) / kTriChunk);
-                return launch_persistent(tri_bwd_kernel<T, W, V, TT>, p, pb, V, TT, kThreads, gz, partial != nullptr, blocks);
+                return launch_persistent(tri_bwd_kernel<T, W, V, TT>, p, pb, V, TT, 512, gz, partial != nullptr, blocks);
             }
         });
     });

@@ -119,6 +119,38 @@ def stage_case(name, reference_module, *, seed, patch, c, events):
           cells_of_x=model._high_to_cells(x))
 
 
+def model_case(name, *, seed, depth, hidden, heads, patch):
+    """The reference's own sublayer-wise model (tiny), unfused reference schedule, forward + backward on CPU."""
+    from sihc.models.sihc.reference import enable_reference_schedule
+    from sihc.models.sihc.sublayer import SublayerSiHCModel
+    torch.manual_seed(seed)
+    model = SublayerSiHCModel(hidden_size=hidden, num_heads=heads, depth=depth, fused_stage_size=depth,
+                              patch_size=patch, attn_backend="math")
+    with torch.no_grad():   # non-zero gates, as research/tests/test_sublayer_kernels.py:229-242
+        for block in model.blocks:
+            block.branch.adaLN_modulation[-1].weight.normal_(std=0.01)
+            block.branch.adaLN_modulation[-1].bias.normal_(std=0.03)
+            for c in (block.attention_connection, block.mlp_connection):
+                c.read_weight.add_(torch.randn_like(c.read_weight) * 0.01)
+                c.write_weight.add_(torch.randn_like(c.write_weight) * 0.02)
+        model.final_layer.linear.weight.normal_(std=0.03)
+        model.final_layer.adaLN_modulation[-1].weight.normal_(std=0.01)
+    enable_reference_schedule(model)
+    gen = torch.Generator().manual_seed(1234)     # inputs come from their own generator so tests can rebuild them
+    x = torch.randn(2, 3, 256, 256, generator=gen)
+    t = torch.rand(2, generator=gen)
+    y = torch.tensor([3, 977])
+    out = model(x, t, y)
+    out.float().square().mean().backward()
+    state = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    grads = {"grad::" + k: p.grad.detach().clone() for k, p in model.named_parameters()
+             if ("connection" in k or k.startswith("final_layer.linear") or "blocks.0.branch.attn.qkv" in k
+                 or k.startswith("x_embedder"))}
+    meta = dict(seed=seed, depth=depth, hidden=hidden, heads=heads, patch=patch, stride=7,
+                source="sihc SublayerSiHCModel + enable_reference_schedule, CPU fp32")
+    _save(name, meta, t=t, y=y.float(), x_sample=x.flatten()[::7], out_sample=out.detach().flatten()[::7], **state, **grads)
+
+
 def main(reference_root: str) -> None:
     sys.path[:0] = [reference_root, os.path.join(reference_root, "sihc")]
     from sihc.bench import fusion_controls as fc
@@ -143,6 +175,7 @@ def main(reference_root: str) -> None:
         tri_case(f"tri_a23_{tag}", fc, seed=583, shape=(1, 49, 67), active=23, dtype=dt, gamma_fp32=(dt == bf16))
     stage_case("stage_p8", reference_module, seed=7, patch=8, c=5, events=3)
     stage_case("stage_p4", reference_module, seed=8, patch=4, c=3, events=4)
+    model_case("model_tiny", seed=19, depth=8, hidden=32, heads=4, patch=8)
 
 
 if __name__ == "__main__":

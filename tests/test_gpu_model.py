@@ -1,0 +1,99 @@
+"""Model-level parity on the GPU: the fused CUDA routing inside ``SublayerSiHC`` against the
+reference model's own output/gradients (fixture) and against the literal dense-carrier oracle."""
+
+import copy
+
+import pytest
+import torch
+
+from conftest import load_golden
+from test_model_cpu import build_from_golden, golden_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def test_fused_model_matches_reference_fixture_fp32():
+    meta, t, model = build_from_golden()
+    x, tt, y = golden_inputs(meta, t)
+    model = model.cuda()
+    out = model(x.cuda(), tt.cuda(), y.cuda())
+    torch.testing.assert_close(out.flatten()[::meta["stride"]].cpu(), t["out_sample"], atol=3e-5, rtol=3e-4)
+    out.float().square().mean().backward()
+    checked = 0
+    for name, p in model.named_parameters():
+        key = "grad::" + name
+        if key in t:
+            torch.testing.assert_close(p.grad.cpu(), t[key], atol=3e-5, rtol=3e-3, msg=name)
+            checked += 1
+    assert checked >= 30
+
+
+@pytest.mark.parametrize("patch,depth,stages", [(8, 8, (8,)), (4, 4, (4,)), (8, 6, (2, 4))])
+def test_fused_model_bf16_autocast_vs_literal_oracle(patch, depth, stages):
+    """bf16 autocast as in training; tolerances of research/tests/test_sublayer_kernels.py:245-263."""
+    from oracle import sihc_model_oracle as MO
+    from residual_stream_burden_b200.model import SublayerSiHC
+    torch.manual_seed(19)
+    model = SublayerSiHC(hidden_size=32, num_heads=4, depth=depth, stage_sizes=stages, patch_size=patch)
+    model.open_gates()
+    ref = copy.deepcopy(model)
+    model = model.cuda()
+    x = torch.randn(1, 3, 256, 256)
+    tt, y = torch.rand(1), torch.zeros(1, dtype=torch.long)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = model(x.cuda(), tt.cuda(), y.cuda())
+    with torch.autocast("cpu", dtype=torch.bfloat16):
+        expect = MO.literal_forward(ref, x, tt, y)
+    out.float().square().mean().backward()
+    expect.float().square().mean().backward()
+    torch.testing.assert_close(out.float().cpu(), expect.float(), atol=0.025, rtol=0.03)
+    for (name, a), (_, b) in zip(model.named_parameters(), ref.named_parameters()):
+        assert a.grad is not None and torch.isfinite(a.grad).all(), name
+        if "connection" in name:
+            rel = (a.grad.cpu() - b.grad).norm() / b.grad.norm().clamp_min(1e-8)
+            assert rel < 0.15, (name, float(rel))
+
+
+def test_training_step_and_sampler_run():
+    from residual_stream_burden_b200.model import SublayerSiHC, sample_heun, velocity_training_batch
+    torch.manual_seed(3)
+    model = SublayerSiHC(hidden_size=64, num_heads=4, depth=4, stage_sizes=(4,), patch_size=8).cuda()
+    model.open_gates()
+    opt = torch.optim.AdamW(model.parameters(), lr=2e-4, betas=(0.9, 0.95), fused=True)
+    x = torch.randn(4, 3, 256, 256, device="cuda")
+    y = torch.randint(0, 1000, (4,), device="cuda")
+    losses = []
+    for _ in range(3):
+        z, t, v = velocity_training_batch(x)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            pred = model(z, t, y)
+        loss = (pred.float() - v).square().mean()
+        loss.backward()
+        assert all(p.grad is not None for p in model.parameters())
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        losses.append(float(loss))
+    assert all(torch.isfinite(torch.tensor(losses)))
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        img = sample_heun(model, y, steps=3, cfg_scale=2.4, interval=(0.1, 0.9))
+    assert img.shape == (4, 3, 256, 256) and torch.isfinite(img).all()
+
+
+def test_triangular_under_fullgraph_compile():
+    """The ops are opaque custom ops with fake kernels: they must trace under fullgraph compile
+    (research/tests/test_sublayer_kernels.py:185-213)."""
+    import residual_stream_burden_b200 as R
+    torch.manual_seed(583)
+    base = torch.randn(3, 49, 64, device="cuda", requires_grad=True)
+    ups = [torch.randn_like(base).requires_grad_() for _ in range(3)]
+    gamma = (torch.randn(3, 64, device="cuda") * 0.05).requires_grad_()
+
+    def fn(base, ups, gamma):
+        out = R.sublayer_triangular(base, ups, gamma)
+        return out.float().square().mean() + sum(u.float().square().mean() for u in ups)
+
+    eager = torch.autograd.grad(fn(base, ups, gamma), (base, *ups, gamma))
+    compiled = torch.compile(fn, fullgraph=True)
+    got = torch.autograd.grad(compiled(base, ups, gamma), (base, *ups, gamma))
+    for a, b in zip(eager, got):
+        torch.testing.assert_close(a, b, atol=1e-6, rtol=1e-4)

@@ -55,6 +55,8 @@ def parse_args():
                     help="op: the read/write path itself (headline); the others time the SiHC models around it")
     ap.add_argument("--no-models", action="store_true", help="skip the model-level figures added to the op line")
     ap.add_argument("--sample-steps", type=int, default=50)
+    ap.add_argument("--sweep", action="store_true",
+                    help="bandwidth sweep over n in {2,4,8}, width in {768,1152}, tokens 2^12..2^20: one JSON line per point")
     return ap.parse_args()
 
 
@@ -261,6 +263,71 @@ def run_e2e(args, batch, grid, slots, channels, dtype, device, steps):
     return seconds, h2d, d2h, chunk
 
 
+# ------------------------------------------------------------------------------------------ sweep
+def run_sweep(args, device, rank, world):
+    """Forward (read+write) and backward (read bwd + write bwd) bandwidth for every point of the sweep.
+
+    Small points fit in the 126 MB L2, so each point rotates over enough independent buffer sets that
+    the data touched between two uses of a set exceeds 512 MB; GB/s is always algorithmic bytes / time.
+    """
+    import torch.distributed as dist
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    esize = 2 if dtype == torch.bfloat16 else 4
+    peak, peak_kind = load_peaks()
+    grid = 16
+    for slots in (2, 4, 8):
+        for channels in (768, 1152):
+            for log2m in range(12, 21):
+                tokens = 1 << log2m
+                batch = tokens // (grid * grid)
+                units = algorithmic_units(slots)
+                set_bytes = (4 * slots + 4) * tokens * channels * esize       # x, gy, y, dx + dz, gz, z, ddz
+                nsets = max(1, min(64, -(-(512 << 20) // set_bytes)))
+                paths = []
+                for k in range(nsets):
+                    inp = make_inputs(batch, grid, slots, channels, dtype, device, seed=k)
+                    paths.append(DevicePath(inp, batch, grid, slots, channels, dtype))
+                reps = max(3, min(50, (1 << 22) // tokens))
+
+                def timed(names):
+                    for pth in paths:                                            # warm-up: every set once
+                        for n in names:
+                            getattr(pth, n)()
+                    torch.cuda.synchronize()
+                    if world > 1:
+                        dist.barrier()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    for r in range(reps):
+                        pth = paths[r % nsets]
+                        for n in names:
+                            getattr(pth, n)()
+                    b.record()
+                    torch.cuda.synchronize()
+                    ms = a.elapsed_time(b) / reps
+                    if world > 1:
+                        t = torch.tensor([ms], device=device)
+                        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                        ms = float(t.item())
+                    return ms
+
+                fwd_ms = timed(("read_fwd", "write_fwd"))
+                bwd_ms = timed(("read_bwd", "write_bwd"))
+                unit = tokens * channels * esize
+                fwd = world * (units["read_fwd"] + units["write_fwd"]) * unit / fwd_ms / 1e6
+                bwd = world * (units["read_bwd"] + units["write_bwd"]) * unit / bwd_ms / 1e6
+                tot = world * sum(units.values()) * unit / (fwd_ms + bwd_ms) / 1e6
+                if rank == 0:
+                    print(json.dumps({"sweep": True, "n": slots, "channels": channels, "log2_tokens": log2m,
+                                      "n_gpus": world, "dtype": args.dtype, "buffer_sets": nsets,
+                                      "fwd_ms": round(fwd_ms, 4), "bwd_ms": round(bwd_ms, 4),
+                                      "fwd_GBs": round(fwd, 1), "bwd_GBs": round(bwd, 1), "fwd_bwd_GBs": round(tot, 1),
+                                      "frac_of_peak": round(tot / world / peak, 4), "peak": peak,
+                                      "peak_source": peak_kind}), flush=True)
+                del paths
+                torch.cuda.empty_cache()
+
+
 # ------------------------------------------------------------------------------------------ models
 def time_device(fn, steps, warmup, world, device):
     """W untimed + K timed calls, CUDA events on the current stream, barrier on both sides, max over ranks."""
@@ -435,7 +502,13 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     from residual_stream_burden_b200 import _lib
+    from residual_stream_burden_b200.dist import allreduce_weight_grads
 
+    if args.sweep:
+        run_sweep(args, device, rank, world)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.workload != "op":
         sampler = ClockSampler(local_rank)
         if rank == 0:
@@ -458,7 +531,6 @@ def main():
 
     inp = make_inputs(batch, grid, slots, channels, dtype, device, seed=rank)
     path = DevicePath(inp, batch, grid, slots, channels, dtype)
-    grads = torch.empty(2, channels, slots, device=device, dtype=torch.float32)
 
     def step(events=None):
         for k, name in enumerate(DevicePath.STAGES):
@@ -467,10 +539,8 @@ def main():
             getattr(path, name)()
             if events is not None:
                 events[k][1].record()
-        if world > 1:       # data-parallel exchange of the small weight gradients
-            grads[0].copy_(path.dalpha[0])
-            grads[1].copy_(path.dbeta[0])
-            dist.all_reduce(grads)
+        if world > 1:       # data-parallel exchange of the small weight gradients: one NCCL all-reduce
+            allreduce_weight_grads([path.dalpha, path.dbeta])
 
     for _ in range(max(args.warmup, 3)):
         step()

@@ -1,0 +1,71 @@
+"""The multi-rank part of the path on CPU: two gloo ranks shard a batch, compute the weight gradient of
+their shard with the oracle, exchange it with ``allreduce_weight_grads`` and must reproduce the full-batch
+gradient; a rank that fails before the exchange makes the other rank's collective end with an error
+instead of hanging (host-side failure, short timeout)."""
+
+import datetime
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import sihc_oracle as O
+
+
+def _worker(rank, world, port, tmp, fail):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    from residual_stream_burden_b200.dist import allreduce_weight_grads, shard_batch
+    try:
+        torch.manual_seed(0)                                   # same full batch on every rank
+        x = torch.randn(6, 8, 8, 16)
+        alpha = 0.25 + 0.02 * torch.randn(2, 16, 4)
+        g = [torch.randn(6, 16, 16) for _ in range(2)]
+        lo, hi = shard_batch(6, rank, world)
+        if fail and rank == 1:
+            raise RuntimeError("injected host-side failure before the exchange")
+        _, dalpha = O.read_backward(x[lo:hi], [t[lo:hi] for t in g], alpha)
+        parts = [dalpha[0].clone(), dalpha[1].clone()]
+        allreduce_weight_grads(parts, average=False)
+        _, full = O.read_backward(x, g, alpha)
+        torch.testing.assert_close(torch.stack(parts), full, atol=1e-5, rtol=1e-5)
+        open(os.path.join(tmp, f"ok{rank}"), "w").write("ok")
+    except Exception as exc:                                   # noqa: BLE001
+        open(os.path.join(tmp, f"err{rank}"), "w").write(repr(exc))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:                                      # noqa: BLE001
+            pass
+
+
+def _port():
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_two_ranks_reproduce_full_batch_weight_gradient(tmp_path):
+    mp.spawn(_worker, args=(2, _port(), str(tmp_path), False), nprocs=2, join=True)
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists(), list(tmp_path.iterdir())
+
+
+def test_rank_failure_surfaces_as_error_not_hang(tmp_path):
+    mp.spawn(_worker, args=(2, _port(), str(tmp_path), True), nprocs=2, join=True)
+    assert (tmp_path / "err1").exists()
+    assert (tmp_path / "err0").exists() and not (tmp_path / "ok0").exists()   # rank 0's all-reduce raised
+
+
+def test_shard_batch_partitions_exactly():
+    from residual_stream_burden_b200.dist import shard_batch
+    for batch in (1, 7, 32, 255):
+        for world in (1, 2, 4, 8):
+            spans = [shard_batch(batch, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == batch
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    with pytest.raises(ValueError):
+        shard_batch(8, 2, 2)

@@ -6,6 +6,10 @@
 
 #include <atomic>
 #include <cstring>
+#include <map>
+#include <mutex>
+#include <set>
+#include <tuple>
 
 #include "sihc_dispatch.cuh"
 
@@ -28,18 +32,58 @@ int sm_count() {
     return cached[dev];
 }
 
+namespace {
+std::mutex g_cache_mutex;
+std::map<std::tuple<int, const void*, int, size_t>, int> g_occupancy;
+std::set<std::pair<int, const void*>> g_smem_raised;
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+    return dev;
+}
+}  // namespace
+
+int cached_occupancy(const void* kernel, int threads, size_t dynamic_smem) {
+    const auto key = std::make_tuple(current_device(), kernel, threads, dynamic_smem);
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    auto it = g_occupancy.find(key);
+    if (it != g_occupancy.end()) return it->second;
+    int nb = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kernel, threads, dynamic_smem) != cudaSuccess || nb < 1) nb = 1;
+    g_occupancy[key] = nb;
+    return nb;
+}
+
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes) {
+    const auto key = std::make_pair(current_device(), kernel);
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    if (g_smem_raised.count(key)) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (e == cudaSuccess) g_smem_raised.insert(key);
+    return e;
+}
+
 static std::atomic<uint64_t> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
 
 uint32_t partial_blocks_bound(uint32_t M) {
     const int cap = tuning().rbps > 0 ? tuning().rbps : 2;
     uint32_t by_sm = static_cast<uint32_t>(sm_count()) * static_cast<uint32_t>(cap);
-    uint32_t by_tokens = (M + 63) / 64;      // a block should own at least 64 tokens
+    const uint32_t per = tuning().min_block_tokens > 0 ? static_cast<uint32_t>(tuning().min_block_tokens) : 64u;
+    uint32_t by_tokens = (M + per - 1) / per;      // a block should own at least this many tokens
     if (by_tokens < 1) by_tokens = 1;
     return by_sm < by_tokens ? by_sm : by_tokens;
 }
 
 namespace {
+
+// Async-copy ring defaults for the fused single-event adjoints, from a stages x threads sweep on B200
+// (2^20 tokens, width 768 and 1152, bf16): three stages win everywhere they win at all; deeper rings lose
+// DRAM locality.  read bwd: n=4 6447 vs 6416 GB/s (width 1152: 6436 vs 6215), n=8 6194 vs 5347, n=2 loses.
+// write bwd: n=4 6710 vs 5879, n=8 6608 vs 5849, n=2 6789 (4 stages) vs 6714.
+inline int read_bwd_ring_stages(int S) { const int t = tuning().ring; return t >= 0 ? t : (S >= 4 ? 3 : 0); }
+inline int write_bwd_ring_stages(int S) { const int t = tuning().ring; return t >= 0 ? t : (S >= 4 ? 3 : 4); }
+constexpr int kReadBwdRingThreads = 256, kWriteBwdRingThreads = 384;
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 inline size_t esize(int dtype) { return dtype == SIHC_BF16 ? 2 : 4; }
@@ -144,6 +188,9 @@ int sihc_tune(const char* name, int value) {
     else if (!std::strcmp(name, "blocks_per_sm")) t.bps = value;
     else if (!std::strcmp(name, "partial_blocks_per_sm")) t.rbps = value;
     else if (!std::strcmp(name, "max_vector_bytes")) t.maxvec_bytes = value;
+    else if (!std::strcmp(name, "ring_stages")) t.ring = value;          // 0 = register-staged kernels
+    else if (!std::strcmp(name, "ring_default")) t.ring = -1;            // back to the per-kernel default
+    else if (!std::strcmp(name, "min_block_tokens")) t.min_block_tokens = value;
     else return SIHC_ERR_NULL;
     return SIHC_OK;
 }
@@ -213,7 +260,10 @@ int sihc_read_bwd(const void* x, const void* const* g, const void* alpha, void* 
     float* partial = dalpha ? static_cast<float*>(workspace) : nullptr;
     uint32_t blocks = 0;
     cudaError_t e;
-    if (events == 1) {
+    const int ring = read_bwd_ring_stages(pb.S);
+    if (events == 1 && ring > 0 && pb.V > 1) {
+        e = launch_read_bwd1_ring(pb, x, g[0], alpha, dx, partial, &blocks, ring, kReadBwdRingThreads);
+    } else if (events == 1) {
         e = launch_read_bwd1(pb, x, g[0], alpha, dx, partial, &blocks);
     } else {
         e = cudaSuccess;
@@ -250,7 +300,11 @@ int sihc_write_bwd(const void* h, const void* const* dz, const void* beta, void*
     float* partial = dbeta ? static_cast<float*>(workspace) : nullptr;
     uint32_t blocks = 0;
     cudaError_t e;
-    if (events == 1) {
+    const int ring = write_bwd_ring_stages(pb.S);
+    if (events == 1 && ring > 0 && pb.V > 1) {
+        e = launch_write_bwd1_ring(pb, h, dbeta ? dz[0] : nullptr, beta, want_ddz ? ddz[0] : nullptr, partial, &blocks, ring,
+                                   kWriteBwdRingThreads);
+    } else if (events == 1) {
         e = launch_write_bwd1(pb, h, dbeta ? dz[0] : nullptr, beta, want_ddz ? ddz[0] : nullptr, partial, &blocks);
     } else {
         e = cudaSuccess;

@@ -81,4 +81,40 @@ inline cudaError_t launch_persistent(K kernel, P& params, const Problem& pb, int
     return cudaGetLastError();
 }
 
+// Variant for kernels that stage their loads in dynamic shared memory, `smem_per_thread` bytes per thread.
+// The block is shrunk (fewer token lanes) until its ring fits the 227 KB a block may use.
+template <typename K, typename P>
+inline cudaError_t launch_persistent_smem(K kernel, P& params, const Problem& pb, int V, int default_threads,
+                                          size_t smem_per_thread, bool emits_partials, uint32_t* gx_out) {
+    constexpr size_t kMaxDynamic = 200 * 1024;     // leaves room for the static reduction buffer
+    const Tuning& tn = tuning();
+    const uint32_t ncv = pb.C / static_cast<uint32_t>(V);
+    BlockShape bs = block_shape(ncv, tn.threads > 0 ? tn.threads : default_threads);
+    while (bs.tl > 1 && static_cast<size_t>(bs.threads) * smem_per_thread > kMaxDynamic) { --bs.tl; bs.threads = bs.cl * bs.tl; }
+    const size_t smem = static_cast<size_t>(bs.threads) * smem_per_thread;
+    if (smem > kMaxDynamic) return cudaErrorInvalidConfiguration;
+    if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kMaxDynamic)) return e;
+    Tiling& t = params.t;
+    t.M = pb.M; t.g = pb.g; t.C = pb.C; t.ncv = ncv; t.cl = bs.cl; t.tl = bs.tl;
+    t.ntiles = (pb.M + bs.tl - 1) / bs.tl;          // one token per thread per ring stage
+    int nb = cached_occupancy(reinterpret_cast<const void*>(kernel), static_cast<int>(bs.threads), smem);
+    uint32_t gx;
+    if (emits_partials) {
+        const int cap = tn.rbps > 0 ? tn.rbps : 2;
+        if (nb > cap) nb = cap;
+        gx = static_cast<uint32_t>(sm_count()) * static_cast<uint32_t>(nb) / bs.gy;
+        const uint32_t bound = partial_blocks_bound(pb.M);
+        if (gx > bound) gx = bound;
+    } else {
+        if (tn.bps > 0 && nb > tn.bps) nb = tn.bps;
+        gx = static_cast<uint32_t>(sm_count()) * static_cast<uint32_t>(nb) / bs.gy;
+    }
+    if (gx < 1) gx = 1;
+    if (gx > t.ntiles) gx = t.ntiles;
+    if (gx_out) *gx_out = gx;
+    kernel<<<dim3(gx, bs.gy, 1), bs.threads, smem, pb.stream>>>(params);
+    count_launch();
+    return cudaGetLastError();
+}
+
 }  // namespace sihc

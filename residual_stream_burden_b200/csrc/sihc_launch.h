@@ -18,6 +18,8 @@ struct Tuning {
     int bps = 0;            // blocks per SM cap for streaming kernels (0: occupancy)
     int rbps = 0;           // blocks per SM for kernels that emit partial sums (0: default 2)
     int maxvec_bytes = 0;   // cap on the vector width in bytes (0: 16)
+    int ring = -1;          // stages of the async-copy ring in the fused single-event adjoints (-1: default, 0: off)
+    int min_block_tokens = 0;   // fewest tokens a partial-sum block should own (0: default)
 };
 Tuning& tuning();
 int sm_count();
@@ -43,6 +45,13 @@ cudaError_t launch_read_bwd1(const Problem& pb, const void* x, const void* g, co
                              float* partial, uint32_t* blocks);
 cudaError_t launch_write_bwd1(const Problem& pb, const void* h, const void* dz, const void* beta, void* ddz,
                               float* partial, uint32_t* blocks);
+// Same contracts, loads staged through a per-thread cp.async ring in shared memory (vector path only).
+cudaError_t launch_read_bwd1_ring(const Problem& pb, const void* x, const void* g, const void* alpha, void* dx,
+                                  float* partial, uint32_t* blocks, int stages, int threads);
+cudaError_t launch_write_bwd1_ring(const Problem& pb, const void* h, const void* dz, const void* beta, void* ddz,
+                                   float* partial, uint32_t* blocks, int stages, int threads);
+struct ReadBwd1Params { const void* x; const void* g; const void* w; void* dx; float* partial; Tiling t; };
+struct WriteBwd1Params { const void* h; const void* dz; const void* w; void* ddz; float* partial; Tiling t; };
 // Multi-event weight gradient partials: [P][E][S][C].
 cudaError_t launch_wgrad(const Problem& pb, const void* carrier, const void* const* z, float* partial,
                          uint32_t* blocks);
@@ -70,15 +79,15 @@ inline BlockShape block_shape(uint32_t ncv, int target_threads) {
     return b;
 }
 
+// Resident blocks per SM of `kernel` at this block size / dynamic shared memory (cached per device,
+// kernel address, block size and shared-memory size; defined in sihc_capi.cu).
+int cached_occupancy(const void* kernel, int threads, size_t dynamic_smem);
+// Raise the kernel's dynamic shared-memory limit once per device.
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes);
+
 template <typename K>
 inline int occupancy_blocks(K kernel, int threads) {
-    static int cache[kMaxThreads + 1];   // one table per kernel instantiation; 0 = unknown
-    int v = cache[threads];
-    if (v == 0) {
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, kernel, threads, 0) != cudaSuccess || v < 1) v = 1;
-        cache[threads] = v;
-    }
-    return v;
+    return cached_occupancy(reinterpret_cast<const void*>(kernel), threads, 0);
 }
 
 }  // namespace sihc

@@ -17,8 +17,6 @@ namespace sihc {
 
 struct ReadFwdParams { const void* x; const void* w; MutPtrs out; int E; Tiling t; };
 struct WriteFwdParams { const void* x; ConstPtrs dz; const void* w; void* y; int E; Tiling t; };
-struct ReadBwd1Params { const void* x; const void* g; const void* w; void* dx; float* partial; Tiling t; };
-struct WriteBwd1Params { const void* h; const void* dz; const void* w; void* ddz; float* partial; Tiling t; };
 
 
 // ---- stage read, forward ---------------------------------------------------------------------
@@ -152,23 +150,32 @@ __global__ void __launch_bounds__(kMaxThreads) write_fwd_kernel(const __grid_con
                 }
             }
 #pragma unroll 1
-            for (int l = 0; l < p.E; ++l) {
-                if (p.dz.p[l] == nullptr) continue;
-                const T* __restrict__ dz = static_cast<const T*>(p.dz.p[l]) + ln.c0;
-                Raw dr[TT];
+            for (int l0 = 0; l0 < p.E; l0 += 4) {           // four update streams in flight per trip
+                Raw dr[4][TT];
+                bool have[4];
 #pragma unroll
-                for (int i = 0; i < TT; ++i)
-                    dr[i] = m[i] < t.M ? IO::load_raw(dz + static_cast<size_t>(m[i]) * t.C) : IO::zero_raw();
-                float w[S][V];
-                load_coeffs<W, S, V>(wt + static_cast<size_t>(l) * t.C * S, w);
+                for (int k = 0; k < 4; ++k) {
+                    const int l = l0 + k;
+                    have[k] = l < p.E && p.dz.p[l] != nullptr;      // a null update is skipped
+                    const T* __restrict__ dz = have[k] ? static_cast<const T*>(p.dz.p[l]) + ln.c0 : nullptr;
 #pragma unroll
-                for (int i = 0; i < TT; ++i) {
-                    float d[V];
-                    IO::unpack(dr[i], d);
+                    for (int i = 0; i < TT; ++i)
+                        dr[k][i] = (have[k] && m[i] < t.M) ? IO::load_raw(dz + static_cast<size_t>(m[i]) * t.C) : IO::zero_raw();
+                }
 #pragma unroll
-                    for (int s = 0; s < S; ++s)
+                for (int k = 0; k < 4; ++k) {
+                    if (!have[k]) continue;
+                    float w[S][V];
+                    load_coeffs<W, S, V>(wt + static_cast<size_t>(l0 + k) * t.C * S, w);
 #pragma unroll
-                        for (int v = 0; v < V; ++v) acc[i][s][v] = fmaf(w[s][v], d[v], acc[i][s][v]);
+                    for (int i = 0; i < TT; ++i) {
+                        float d[V];
+                        IO::unpack(dr[k][i], d);
+#pragma unroll
+                        for (int s = 0; s < S; ++s)
+#pragma unroll
+                            for (int v = 0; v < V; ++v) acc[i][s][v] = fmaf(w[s][v], d[v], acc[i][s][v]);
+                    }
                 }
             }
 #pragma unroll
@@ -328,7 +335,7 @@ cudaError_t launch_read_fwd(const Problem& pb, const void* x, const void* alpha,
                 constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
                 if (pb.E == 1)
                     return launch_persistent(read_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kReadFwdThreads, 1, false, nullptr);
-                return launch_persistent(read_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, 384, 1, false, nullptr);
+                return launch_persistent(read_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, 512, 1, false, nullptr);
             });
         });
     });
@@ -346,7 +353,7 @@ cudaError_t launch_write_fwd(const Problem& pb, const void* x, const void* const
                 constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
                 if (pb.E == 1 && dz[0] != nullptr)
                     return launch_persistent(write_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kWriteFwdThreads, 1, false, nullptr);
-                return launch_persistent(write_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, kWriteFwdThreads, 1, false, nullptr);
+                return launch_persistent(write_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, 512, 1, false, nullptr);
             });
         });
     });

@@ -309,3 +309,30 @@ def test_c_abi_direct_calls_and_status_codes(R):
     assert lib.sihc_read_fwd(*args, _lib.F32, _lib.F32, s) == 0
     assert _lib.launch_count() == before + 1
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("stages", [0, 3, 4, 8])
+@pytest.mark.parametrize("slots,dtype", [(4, torch.bfloat16), (8, torch.bfloat16), (2, torch.float32), (16, torch.bfloat16)])
+def test_single_event_adjoints_register_and_ring_variants(R, stages, slots, dtype):
+    """The fused single-event adjoints exist in two forms (loads staged in registers, or through a
+    shared-memory async-copy ring); both must give the same answer, including ragged token counts."""
+    from residual_stream_burden_b200 import _lib
+    torch.manual_seed(77 + slots)
+    kh, kw = O.cell_shape(slots)
+    b, g, c = 5, 7, 128                                   # 245 tokens: not a multiple of any tile
+    x = torch.randn(b, g * kh, g * kw, c).to(dtype)
+    alpha = (1.0 / slots + 0.05 * torch.randn(1, c, slots)).to(dtype)
+    dz = [torch.randn(b, g * g, c).to(dtype)]
+    gz = [torch.randn(b, g * g, c).to(dtype)]
+    gy = torch.randn(b, g * kh, g * kw, c).to(dtype)
+    _lib.tune("ring_stages", stages)
+    try:
+        got = run_all(R, x, alpha, alpha, dz, gz, gy)
+    finally:
+        _lib.tune("ring_default", 0)
+    odx, oda = O.read_backward(x, gz, alpha, acc=torch.float64)
+    oddz, odb = O.write_backward(gy, dz, alpha, acc=torch.float64)
+    close(got["dx_read"], odx, dtype, "dx_read")
+    close(got["ddz"], torch.stack(oddz), dtype, "ddz")
+    close(got["dalpha"], oda.to(dtype), dtype, "dalpha")
+    close(got["dbeta"], odb.to(dtype), dtype, "dbeta")

@@ -51,10 +51,13 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=2)
-    ap.add_argument("--workload", default="op", choices=["op", "sihc_b_fwd", "sihc_xl_train", "sihc_xl_sample"],
+    ap.add_argument("--workload", default="op", choices=["op", "stage_ops", "sihc_b_fwd", "sihc_xl_train", "sihc_xl_sample"],
                     help="op: the read/write path itself (headline); the others time the SiHC models around it")
     ap.add_argument("--no-models", action="store_true", help="skip the model-level figures added to the op line")
     ap.add_argument("--sample-steps", type=int, default=50)
+    ap.add_argument("--events", type=int, default=24, help="events per stage for --workload stage_ops")
+    ap.add_argument("--no-compile", action="store_true",
+                    help="run the models' torch sublayers eagerly instead of under torch.compile")
     ap.add_argument("--sweep", action="store_true",
                     help="bandwidth sweep over n in {2,4,8}, width in {768,1152}, tokens 2^12..2^20: one JSON line per point")
     return ap.parse_args()
@@ -156,8 +159,10 @@ class DevicePath:
         self.y = torch.empty_like(inp["x"])
         self.dx = torch.empty_like(inp["x"])
         self.ddz = torch.empty_like(inp["dz"])
-        self.dalpha = torch.empty(1, channels, slots, device=dev, dtype=torch.float32)
-        self.dbeta = torch.empty(1, channels, slots, device=dev, dtype=torch.float32)
+        # both weight gradients are written by the kernels straight into ONE flat fp32 buffer, so that the
+        # data-parallel exchange is a single all-reduce with no packing copies
+        self.wgrads = torch.empty(2, 1, channels, slots, device=dev, dtype=torch.float32)
+        self.dalpha, self.dbeta = self.wgrads[0], self.wgrads[1]
         nbytes = self.lib.sihc_wgrad_workspace_bytes(1, batch, grid, kh, kw, channels, self.dt)
         self.ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
         pa = _lib.ptr_array
@@ -328,6 +333,75 @@ def run_sweep(args, device, rank, world):
                 torch.cuda.empty_cache()
 
 
+# ------------------------------------------------------------------------------------------ stage ops
+def run_stage_ops(args, device, steps, warmup):
+    """The multi-event stage operators one by one on SiHC-B's stage shapes (BASELINE config 2: batch 256,
+    256 tokens, n=4, width 768, E=24 events): read(E), triangular(E-1), write(E) and their backward calls.
+    GB/s are algorithmic bytes (read S+E, write 2S+E, triangular J+2, read bwd 2(S+E) as two kernels,
+    write bwd 2(S+E), triangular bwd 2J+1) over the CUDA-event time of the C ABI call."""
+    from residual_stream_burden_b200 import _lib
+    lib = _lib.lib
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    code = _lib.BF16 if dtype == torch.bfloat16 else _lib.F32
+    esize = 2 if dtype == torch.bfloat16 else 4
+    S, C, E, g = args.slots, args.channels, args.events, 16
+    kh, kw = CELLS[S]
+    tokens = 1 << min(args.log2_tokens, 16)
+    B = tokens // 256
+    gen = torch.Generator(device=device).manual_seed(0)
+
+    def rnd(*shape, std=1.0, mean=0.0):
+        return torch.empty(*shape, device=device, dtype=dtype).normal_(mean, std, generator=gen)
+
+    x, gy, y = rnd(B, g * kh, g * kw, C), rnd(B, g * kh, g * kw, C), torch.empty(B, g * kh, g * kw, C, device=device, dtype=dtype)
+    dz = [rnd(B, 256, C) for _ in range(E)]
+    out = [torch.empty(B, 256, C, device=device, dtype=dtype) for _ in range(E)]
+    w = rnd(E, C, S, std=0.02, mean=1.0 / S)
+    gam = rnd(E, C, std=0.05)
+    dw = torch.empty(E, C, S, device=device, dtype=torch.float32)
+    dgam = torch.empty(E, C, device=device, dtype=torch.float32)
+    nbytes = max(lib.sihc_wgrad_workspace_bytes(E, B, g, kh, kw, C, code), lib.sihc_tri_workspace_bytes(E, tokens, C, code), 16)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    st = torch.cuda.current_stream().cuda_stream
+    pa = _lib.ptr_array
+    p_dz, p_out = pa([t.data_ptr() for t in dz]), pa([t.data_ptr() for t in out])
+    geom = (B, g, kh, kw, C, code, code, st)
+    J = E - 1 if E > 1 else 1
+    ops = {
+        "read_fwd": (lambda: lib.sihc_read_fwd(x.data_ptr(), w.data_ptr(), p_out, E, *geom), S + E),
+        "triangular_fwd": (lambda: lib.sihc_tri_fwd(out[0].data_ptr(), p_dz, gam.data_ptr(), y.data_ptr(), J, tokens, C, code, code, st), J + 2),
+        "write_fwd": (lambda: lib.sihc_write_fwd(x.data_ptr(), p_dz, w.data_ptr(), y.data_ptr(), E, *geom), 2 * S + E),
+        "write_bwd": (lambda: lib.sihc_write_bwd(gy.data_ptr(), p_dz, w.data_ptr(), p_out, dw.data_ptr(), ws.data_ptr(), ws.numel(), E, *geom), 2 * (S + E)),
+        "triangular_bwd": (lambda: lib.sihc_tri_bwd(out[0].data_ptr(), p_dz, gam.data_ptr(), p_out, dgam.data_ptr(), ws.data_ptr(), ws.numel(), J, tokens, C, code, code, st), 2 * J + 1),
+        "read_bwd": (lambda: lib.sihc_read_bwd(x.data_ptr(), p_dz, w.data_ptr(), y.data_ptr(), dw.data_ptr(), ws.data_ptr(), ws.numel(), E, *geom), 2 * (S + E)),
+    }
+    peak, peak_kind = load_peaks()
+    res = {}
+    launches0 = _lib.launch_count()
+    for name, (fn, units) in ops.items():
+        for _ in range(warmup):
+            _lib.check(fn(), name)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / steps
+        gbs = units * tokens * C * esize / ms / 1e6
+        res[name] = {"ms": round(ms, 4), "units": units, "GB/s": round(gbs, 1), "frac": round(gbs / peak, 4)}
+    total_ms = sum(v["ms"] for v in res.values())
+    total_units = sum(v["units"] for v in res.values())
+    value = total_units * tokens * C * esize / total_ms / 1e6
+    print(json.dumps({"metric": "sihc_stage_ops_bandwidth", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1,
+                      "steps": steps, "warmup": warmup, "ms_per_step": round(total_ms, 4), "higher_is_better": True,
+                      "dtype": args.dtype, "data": "synthetic",
+                      "config": {"workload": f"stage operators, E={E} events, n={S}, width {C}, {tokens} tokens"},
+                      "peak": peak, "peak_source": peak_kind, "ops": res,
+                      "gpu_launches": int(_lib.launch_count() - launches0)}))
+
+
 # ------------------------------------------------------------------------------------------ models
 def time_device(fn, steps, warmup, world, device):
     """W untimed + K timed calls, CUDA events on the current stream, barrier on both sides, max over ranks."""
@@ -353,10 +427,15 @@ def time_device(fn, steps, warmup, world, device):
     return ms / steps
 
 
-def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_steps=50):
+def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_steps=50, compile_model=True):
     """SiHC-B forward (batch 256), SiHC-XL training step (batch 32 per GPU, DDP) or SiHC-XL Heun sampling
     (batch 256 per GPU, CFG 2.4 on [0.1, 0.9]); bf16 autocast over fp32 parameters, synthetic N(0,1) images,
-    random-init weights with opened gates.  Inputs start in pinned host memory every step."""
+    random-init weights with opened gates.  Inputs start in pinned host memory every step.
+
+    As in the reference's own benchmark (compile, then DDP: sihc/bench/fusion_profile.py:113-195) the model runs
+    under ``torch.compile(fullgraph=True)``; that fuses the torch sublayers' elementwise glue (norms, modulation,
+    RoPE, gates).  The routing operators stay opaque ``sihc_b200::*`` custom ops inside the graph: every read,
+    write and triangular step is this package's CUDA kernel either way."""
     from residual_stream_burden_b200 import _lib
     from residual_stream_burden_b200.model import sample_heun, sihc_b, sihc_xl, velocity_training_batch
     torch.backends.cuda.matmul.allow_tf32 = True
@@ -368,6 +447,7 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         batch = 256
         model = sihc_b().to(device).eval()
         model.open_gates()
+        net = torch.compile(model, fullgraph=True) if compile_model else model
         x_host = torch.randn(batch, 3, 256, 256, generator=gen).pin_memory()
         t = torch.rand(batch, device=device)
         y = torch.randint(0, 1000, (batch,), device=device)
@@ -375,7 +455,7 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         def step():
             x = x_host.to(device, non_blocking=True)
             with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
-                out = model(x, t, y)
+                out = net(x, t, y)
             return float(out.float().abs().mean())          # device -> host read of a scalar
 
         ms = time_device(step, steps, warmup, world, device)
@@ -384,10 +464,10 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         batch = 32
         model = sihc_xl().to(device)
         model.open_gates()
-        net = model
+        net = torch.compile(model, fullgraph=True) if compile_model else model
         if world > 1:
             from torch.nn.parallel import DistributedDataParallel as DDP
-            net = DDP(model, device_ids=[local_rank], gradient_as_bucket_view=True)
+            net = DDP(net, device_ids=[local_rank], gradient_as_bucket_view=True)
         opt = torch.optim.AdamW(model.parameters(), lr=2e-4, betas=(0.9, 0.95), weight_decay=0.0, fused=True)
         x_host = torch.randn(batch, 3, 256, 256, generator=gen).pin_memory()
         y = torch.randint(0, 1000, (batch,), device=device)
@@ -401,7 +481,7 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
             loss.backward()
             opt.step()
             opt.zero_grad(set_to_none=True)
-            return float(loss)                              # device -> host read of the loss
+            return float(loss.detach())                     # device -> host read of the loss
 
         ms = time_device(step, steps, warmup, world, device)
         name = "SiHC-XL training step, 28 blocks x 1152, n=4, stages 8+12+8, batch 32 per GPU, bf16 autocast + fp32 AdamW"
@@ -409,16 +489,18 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         batch = 256
         model = sihc_xl().to(device).eval()
         model.open_gates()
+        net = torch.compile(model, fullgraph=True) if compile_model else model
         y = torch.randint(0, 1000, (batch,), device=device)
 
         def step():
             with torch.autocast("cuda", dtype=torch.bfloat16):
-                img = sample_heun(model, y, steps=sample_steps, cfg_scale=2.4, interval=(0.1, 0.9))
+                img = sample_heun(net, y, steps=sample_steps, cfg_scale=2.4, interval=(0.1, 0.9))
             return float(img.float().abs().mean())
 
         ms = time_device(step, steps, warmup, world, device)
         name = f"SiHC-XL Heun sampling, {sample_steps} steps, CFG 2.4 on [0.1,0.9], batch 256 per GPU, bf16 autocast"
     launches = _lib.launch_count() - launches0
+    name += ", torch.compile around the torch sublayers" if compile_model else ", eager"
     res = {"workload": name, "img_per_s": round(world * batch / (ms * 1e-3), 2), "ms_per_step": round(ms, 3),
            "global_batch": world * batch, "routing_launches_per_step": launches // max(1, steps + warmup),
            "peak_mem_gb": round(torch.cuda.max_memory_allocated(device) / 2**30, 2)}
@@ -502,10 +584,15 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     from residual_stream_burden_b200 import _lib
-    from residual_stream_burden_b200.dist import allreduce_weight_grads
 
     if args.sweep:
         run_sweep(args, device, rank, world)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.workload == "stage_ops":
+        if rank == 0:
+            run_stage_ops(args, device, args.steps, max(args.warmup, 3))
         if world > 1:
             dist.destroy_process_group()
         return
@@ -514,7 +601,7 @@ def main():
         if rank == 0:
             sampler.start()
         res = model_workload(args.workload, device, rank, world, local_rank, args.steps, max(args.warmup, 3),
-                             args.sample_steps)
+                             args.sample_steps, not args.no_compile)
         clocks = sampler.stop() if rank == 0 else None
         if rank == 0:
             print(json.dumps({"metric": args.workload + "_throughput", "value": res["img_per_s"], "unit": "img/s",
@@ -540,7 +627,8 @@ def main():
             if events is not None:
                 events[k][1].record()
         if world > 1:       # data-parallel exchange of the small weight gradients: one NCCL all-reduce
-            allreduce_weight_grads([path.dalpha, path.dbeta])
+            dist.all_reduce(path.wgrads)
+            path.wgrads.div_(world)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -618,9 +706,10 @@ def main():
         # second half of the headline metric: the models around the path, same process, same GPUs
         del path, inp
         torch.cuda.empty_cache()
-        models = {"sihc_xl_train": model_workload("sihc_xl_train", device, rank, world, local_rank, 5, 3)}
+        cm = not args.no_compile
+        models = {"sihc_xl_train": model_workload("sihc_xl_train", device, rank, world, local_rank, 5, 3, 50, cm)}
         if world == 1:
-            models["sihc_b_fwd"] = model_workload("sihc_b_fwd", device, rank, world, local_rank, 5, 3)
+            models["sihc_b_fwd"] = model_workload("sihc_b_fwd", device, rank, world, local_rank, 5, 3, 50, cm)
 
     if rank == 0:
         line = {"metric": "sihc_read_write_fwd_bwd_bandwidth", "value": round(value, 1), "unit": "GB/s",

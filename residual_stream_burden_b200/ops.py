@@ -319,6 +319,10 @@ def _tri_backward(ctx, grad):
     need_base, need_u, need_g = ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2]
     grad = grad.contiguous()
     ddz, dgamma = None, None
+    # The per-edge products ddz_l = grad * gamma_l are produced by the kernel (one pass over grad for all
+    # edges).  Leaving them to the compiler as torch ops, as the reference does
+    # (sihc/models/sihc/sublayer_kernels.py:373-379), was measured slower here: 94.6 vs 60.5 ms per
+    # SiHC-XL training step on B200.
     if need_u or need_g:
         ddz_list, dgamma_t = _tri_backward_op(grad, updates, gamma, bool(need_u), bool(need_g))
         ddz = ddz_list if need_u else None

@@ -447,6 +447,7 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         batch = 256
         model = sihc_b().to(device).eval()
         model.open_gates()
+        model.inference_schedule = "literal"        # n = 4: fused write+read steps move fewer bytes than the factored stage
         net = torch.compile(model, fullgraph=True) if compile_model else model
         x_host = torch.randn(batch, 3, 256, 256, generator=gen).pin_memory()
         t = torch.rand(batch, device=device)
@@ -459,7 +460,7 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
             return float(out.float().abs().mean())          # device -> host read of a scalar
 
         ms = time_device(step, steps, warmup, world, device)
-        name = "SiHC-B forward, 12 blocks x 768, n=4, batch 256 per GPU, bf16 autocast"
+        name = "SiHC-B forward, 12 blocks x 768, n=4, batch 256 per GPU, bf16 autocast, literal fused write+read schedule"
     elif kind == "sihc_xl_train":
         batch = 32
         model = sihc_xl().to(device)
@@ -489,6 +490,7 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         batch = 256
         model = sihc_xl().to(device).eval()
         model.open_gates()
+        model.inference_schedule = "literal"
         net = torch.compile(model, fullgraph=True) if compile_model else model
         y = torch.randint(0, 1000, (batch,), device=device)
 
@@ -498,7 +500,7 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
             return float(img.float().abs().mean())
 
         ms = time_device(step, steps, warmup, world, device)
-        name = f"SiHC-XL Heun sampling, {sample_steps} steps, CFG 2.4 on [0.1,0.9], batch 256 per GPU, bf16 autocast"
+        name = f"SiHC-XL Heun sampling, {sample_steps} steps, CFG 2.4 on [0.1,0.9], batch 256 per GPU, bf16 autocast, literal fused write+read schedule"
     launches = _lib.launch_count() - launches0
     name += ", torch.compile around the torch sublayers" if compile_model else ", eager"
     res = {"workload": name, "img_per_s": round(world * batch / (ms * 1e-3), 2), "ms_per_step": round(ms, 3),

@@ -81,6 +81,21 @@ int sihc_write_fwd(const void* x, const void* const* dz, const void* beta, void*
                    int dtype, int wdtype, void* stream);
 
 /*
+ * Literal (unfused-schedule) step for inference: write one event into the carrier and read the next
+ * event from the result, in one pass over the carrier.
+ *   y[m,s,c]      = x[m,s,c] + beta[c,s] * dz[m,c]        (rounded to `dtype`)
+ *   z_next[m,c]   = sum_s alpha_next[c,s] * y[m,s,c]      (computed from the rounded y)
+ * `beta` and `alpha_next` are [channels, slots].  Replaces the pair
+ * `carrier = write_torch(carrier, [dz], [beta]); z = read_torch(carrier, alpha_next)` of the reference's
+ * literal schedule (sihc/bench/fusion_controls.py:64, :80; research/tests/test_sublayer_kernels.py:216-226)
+ * and gives the same values, moving 2*slots+2 elements per token and channel instead of 3*slots+2.
+ * `y` may be `x` (in-place carrier update).  Forward only.
+ */
+int sihc_write_read_fwd(const void* x, const void* dz, const void* beta, const void* alpha_next,
+                        void* y, void* z_next, int64_t batch, int grid, int kh, int kw, int channels,
+                        int dtype, int wdtype, void* stream);
+
+/*
  * Bytes of scratch the two backward entry points below need for `events` events
  * on this geometry (per-block partial sums of the weight gradients).  The
  * scratch needs no initialisation and holds nothing between calls.

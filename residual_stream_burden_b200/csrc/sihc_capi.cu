@@ -226,6 +226,19 @@ int sihc_write_fwd(const void* x, const void* const* dz, const void* beta, void*
     return status_of(launch_write_fwd(pb, x, dz, beta, y));
 }
 
+int sihc_write_read_fwd(const void* x, const void* dz, const void* beta, const void* alpha_next, void* y, void* z_next,
+                        int64_t batch, int grid, int kh, int kw, int channels, int dtype, int wdtype, void* stream) {
+    Problem pb;
+    if (int st = make_problem(pb, 1, batch, grid, kh, kw, channels, dtype, wdtype, stream)) return st;
+    if (!x || !dz || !beta || !alpha_next || !y || !z_next) return SIHC_ERR_NULL;
+    VecChoice vc(vec_width(pb.dtype, pb.S), esize(dtype), pb.C);
+    vc.act(x); vc.act(dz); vc.act(y); vc.act(z_next);
+    vc.weight(beta, esize(wdtype)); vc.weight(alpha_next, esize(wdtype));
+    if (!vc.elem_ok) return SIHC_ERR_ALIGN;
+    pb.V = vc.V();
+    return status_of(launch_write_read(pb, x, dz, beta, alpha_next, y, z_next));
+}
+
 size_t sihc_wgrad_workspace_bytes(int events, int64_t batch, int grid, int kh, int kw, int channels, int dtype) {
     Problem pb;
     if (make_problem(pb, events, batch, grid, kh, kw, channels, dtype, dtype, nullptr)) return 0;

@@ -40,6 +40,9 @@ uint32_t partial_blocks_bound(uint32_t M);
 
 cudaError_t launch_read_fwd(const Problem& pb, const void* x, const void* alpha, void* const* out);
 cudaError_t launch_write_fwd(const Problem& pb, const void* x, const void* const* dz, const void* beta, void* y);
+// Literal inference step: y = x + beta*dz (rounded), z_next = read(y, alpha_next); y may alias x.
+cudaError_t launch_write_read(const Problem& pb, const void* x, const void* dz, const void* beta, const void* alpha_next,
+                              void* y, void* z_next);
 // Fused single-event adjoints; `partial` receives [P][S][C] fp32 rows, *blocks = P.
 cudaError_t launch_read_bwd1(const Problem& pb, const void* x, const void* g, const void* alpha, void* dx,
                              float* partial, uint32_t* blocks);

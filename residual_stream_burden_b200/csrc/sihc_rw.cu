@@ -189,6 +189,65 @@ __global__ void __launch_bounds__(kMaxThreads) write_fwd_kernel(const __grid_con
     }
 }
 
+// ---- literal step: write event i, read event i+1, one pass (inference) ------------------------------
+// y[m,s,c] = x[m,s,c] + beta[c,s] * dz[m,c]   (rounded to the storage type, as the unfused path stores it)
+// z[m,c]   = sum_s alpha_next[c,s] * y[m,s,c] (read from the ROUNDED carrier, as the unfused path reads it)
+// Moves 2S+2 elements per (token, channel); the unfused pair moves 3S+2.  `y` may be `x` (in place): every
+// element is read and written by the same thread.
+struct WriteReadParams { const void* x; const void* dz; const void* beta; const void* alpha; void* y; void* z; Tiling t; };
+
+template <typename T, typename W, int S, int V, int TT>
+__global__ void __launch_bounds__(kMaxThreads) write_read_kernel(const __grid_constant__ WriteReadParams p) {
+    typedef VecIO<T, V> IO;
+    typedef typename IO::Raw Raw;
+    const Tiling& t = p.t;
+    const Lane ln = make_lane<V>(t);
+    if (!ln.active) return;
+    const T* x = static_cast<const T*>(p.x) + ln.c0;
+    T* y = static_cast<T*>(p.y) + ln.c0;
+    const T* __restrict__ dz = static_cast<const T*>(p.dz) + ln.c0;
+    T* __restrict__ z = static_cast<T*>(p.z) + ln.c0;
+    float wb[S][V], wa[S][V];
+    load_coeffs<W, S, V>(static_cast<const W*>(p.beta) + static_cast<size_t>(ln.c0) * S, wb);
+    load_coeffs<W, S, V>(static_cast<const W*>(p.alpha) + static_cast<size_t>(ln.c0) * S, wa);
+    const uint32_t per_tile = t.tl * TT;
+    for (uint32_t tile = blockIdx.x; tile < t.ntiles; tile += gridDim.x) {
+        Raw xr[TT][S];
+        Raw dr[TT];
+        uint32_t m[TT];
+        size_t origin[TT];
+#pragma unroll
+        for (int i = 0; i < TT; ++i) {
+            m[i] = tile * per_tile + i * t.tl + ln.tl;
+            const bool ok = m[i] < t.M;
+            origin[i] = cell_origin<S>(ok ? m[i] : 0u, t.g, t.C);
+            dr[i] = ok ? IO::load_raw(dz + static_cast<size_t>(m[i]) * t.C) : IO::zero_raw();
+#pragma unroll
+            for (int s = 0; s < S; ++s) xr[i][s] = ok ? IO::load_raw(x + origin[i] + slot_offset<S>(s, t.g, t.C)) : IO::zero_raw();
+        }
+#pragma unroll
+        for (int i = 0; i < TT; ++i) {
+            float d[V], acc[V];
+            IO::unpack(dr[i], d);
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                float r[V];
+                IO::unpack(xr[i][s], r);
+#pragma unroll
+                for (int v = 0; v < V; ++v) r[v] = fmaf(wb[s][v], d[v], r[v]);
+                if constexpr (sizeof(T) == 2) {             // round to storage before the read uses it
+#pragma unroll
+                    for (int v = 0; v < V; ++v) r[v] = __uint_as_float(static_cast<uint32_t>(pack_bf16(r[v])) << 16);
+                }
+                if (m[i] < t.M) IO::store(y + origin[i] + slot_offset<S>(s, t.g, t.C), r);
+#pragma unroll
+                for (int v = 0; v < V; ++v) acc[v] = s == 0 ? r[v] * wa[0][v] : fmaf(r[v], wa[s][v], acc[v]);
+            }
+            if (m[i] < t.M) IO::store(z + static_cast<size_t>(m[i]) * t.C, acc);
+        }
+    }
+}
+
 // ---- single-event read, backward (fused) ---------------------------------------------------
 // dx[m,s,c] = alpha[c,s] * g[m,c];  partial[block][s][c] = sum_{m in block} X[m,s,c] * g[m,c]
 // One pass over X and g produces both adjoints (the reference makes two passes:
@@ -355,6 +414,23 @@ cudaError_t launch_write_fwd(const Problem& pb, const void* x, const void* const
                     return launch_persistent(write_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kWriteFwdThreads, 1, false, nullptr);
                 return launch_persistent(write_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, 512, 1, false, nullptr);
             });
+        });
+    });
+}
+
+cudaError_t launch_write_read(const Problem& pb, const void* x, const void* dz, const void* beta, const void* alpha_next,
+                              void* y, void* z_next) {
+    WriteReadParams p{};
+    p.x = x; p.dz = dz; p.beta = beta; p.alpha = alpha_next; p.y = y; p.z = z_next;
+    return dispatch_types(pb.dtype, pb.wdtype, [&](auto tt_, auto ww_) {
+        using T = decltype(tt_); using W = decltype(ww_);
+        return dispatch_slots(pb.S, [&](auto s_) {
+            constexpr int S = decltype(s_)::value;
+            constexpr int VM = VecWidth<T, S>::value;
+            // 512 threads x 2 tokens measured best on B200 (n=4, width 768: 5876 GB/s vs 5149 at 384 x 1)
+            if (pb.V == 1) return launch_persistent(write_read_kernel<T, W, S, 1, 1>, p, pb, 1, 1, 512, 1, false, nullptr);
+            if (pick_tt(2) >= 2) return launch_persistent(write_read_kernel<T, W, S, VM, 2>, p, pb, VM, 2, 512, 1, false, nullptr);
+            return launch_persistent(write_read_kernel<T, W, S, VM, 1>, p, pb, VM, 1, 512, 1, false, nullptr);
         });
     });
 }

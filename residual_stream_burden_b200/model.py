@@ -237,6 +237,10 @@ class SublayerSiHC(nn.Module):
         self.workspace_rope = AxialRope(hidden_size // num_heads // 2, workspace_grid)
         self.blocks = nn.ModuleList(SublayerBlock(hidden_size, num_heads, k * k, mlp_ratio) for _ in range(depth))
         self.final_layer = FinalLayer(hidden_size, patch_size, in_channels)
+        # "factored": one read, triangular accumulation, one write per stage (training and default).
+        # "literal": write event i and read event i+1 in one pass over the carrier, no triangular step;
+        # forward-only, fewer bytes than the factored stage when n <= 4 (10 vs ~16 elements per event at E=24).
+        self.inference_schedule = "factored"
         self.reset_parameters()
 
     def reset_parameters(self) -> None:
@@ -296,9 +300,36 @@ class SublayerSiHC(nn.Module):
             updates.append(block.branch.mlp_update(z, mod).contiguous())
         return ops.sublayer_write(x0, updates, beta)
 
+    def run_literal(self, carrier: Tensor, cond: Tensor) -> Tensor:
+        """All events with the literal recurrence (reference definition: ``literal_forward``,
+        research/tests/test_sublayer_kernels.py:216-226), each write fused with the next event's read."""
+        if torch.is_grad_enabled():
+            raise RuntimeError("the literal schedule is forward-only: call it under torch.no_grad()")
+        events = [(block, conn, kind) for block in self.blocks
+                  for conn, kind in ((block.attention_connection, "attn"), (block.mlp_connection, "mlp"))]
+        dtype = carrier.dtype
+        z = ops.sihc_read(carrier, events[0][1].alpha(dtype).contiguous())
+        mod = None
+        for i, (block, conn, kind) in enumerate(events):
+            if kind == "attn":
+                mod = block.branch.conditioning(cond)
+                dz = block.branch.attention_update(z, mod, self.workspace_rope).contiguous()
+            else:
+                dz = block.branch.mlp_update(z, mod).contiguous()
+            if i + 1 < len(events):
+                carrier, z = ops.sihc_write_read(carrier, dz, conn.beta(dtype).contiguous(),
+                                                 events[i + 1][1].alpha(dtype).contiguous())
+            else:
+                carrier = ops.sihc_write(carrier, dz, conn.beta(dtype).contiguous())
+        return carrier
+
     def forward(self, x: Tensor, t: Tensor, y: Tensor) -> Tensor:
         cond = self.t_embedder(t) + self.y_embedder(y)
         carrier = self.x_embedder(x)
+        if self.inference_schedule == "literal" and not torch.is_grad_enabled():
+            carrier = self.run_literal(carrier, cond)
+            b, hh, ww, c = carrier.shape
+            return self.unpatchify(self.final_layer(carrier.reshape(b, hh * ww, c), cond))
         start = 0
         for size in self.stage_sizes:
             carrier = self.run_stage(carrier, cond, self.blocks[start:start + size])

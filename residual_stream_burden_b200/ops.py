@@ -393,6 +393,34 @@ def sihc_write(x: Tensor, dz: Tensor, beta: Tensor) -> Tensor:
     return _SihcWrite.apply(x, dz, beta)
 
 
+@custom_op("sihc_b200::write_read", mutates_args=())
+def sihc_write_read(x: Tensor, dz: Tensor, beta: Tensor, alpha_next: Tensor) -> tuple[Tensor, Tensor]:
+    """One step of the literal schedule for inference: ``Y = X + beta * dz`` and the NEXT event's read
+    ``z = sum_s alpha_next * Y`` in a single pass over the carrier.  Returns ``(Y, z)``.
+
+    ``beta`` and ``alpha_next`` are ``[C, S]``.  Same values as ``write_torch`` followed by ``read_torch``
+    (sihc/bench/fusion_controls.py:14-31): the carrier is rounded to its storage dtype before it is read.
+    Forward only (no autograd formula): use it under ``torch.no_grad()``.
+    """
+    if beta.ndim != 2 or alpha_next.ndim != 2 or beta.shape != alpha_next.shape or beta.dtype != alpha_next.dtype:
+        raise ValueError("expected matching [channels, slots] write and read weights")
+    _require_packed("sublayer write/read", alpha_next=alpha_next)
+    b, c, g, kh, kw = _validate_updates(x, beta.unsqueeze(0), [dz])
+    y = torch.empty_like(x)
+    z = torch.empty((b, g * g, c), device=x.device, dtype=x.dtype)
+    with torch.cuda.device(x.device):
+        check(lib.sihc_write_read_fwd(x.data_ptr(), dz.data_ptr(), beta.data_ptr(), alpha_next.data_ptr(),
+                                      y.data_ptr(), z.data_ptr(), b, g, kh, kw, c,
+                                      _DTYPES[x.dtype], _DTYPES[beta.dtype], _stream(x)), "sihc_write_read_fwd")
+    return y, z
+
+
+@sihc_write_read.register_fake
+def _write_read_fake(x, dz, beta, alpha_next):
+    b, c, g, _, _ = _validate_updates(x, beta.unsqueeze(0), [dz], fake=True)
+    return torch.empty_like(x), x.new_empty((b, g * g, c))
+
+
 # --------------------------------------------------------------------------- block-wise adapters
 def _require_block_events(weights: Tensor) -> None:
     if weights.ndim != 3 or weights.shape[0] not in (8, 12):
@@ -421,5 +449,5 @@ def blockwise_triangular(base: Tensor, updates: List[Tensor], gamma: Tensor) -> 
 __all__ = [
     "sublayer_read", "sublayer_write", "sublayer_triangular",
     "blockwise_read", "blockwise_write", "blockwise_triangular",
-    "sihc_read", "sihc_write",
+    "sihc_read", "sihc_write", "sihc_write_read",
 ]

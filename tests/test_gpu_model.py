@@ -97,3 +97,27 @@ def test_triangular_under_fullgraph_compile():
     got = torch.autograd.grad(compiled(base, ups, gamma), (base, *ups, gamma))
     for a, b in zip(eager, got):
         torch.testing.assert_close(a, b, atol=1e-6, rtol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_literal_inference_schedule_matches_oracle_and_factored(dtype):
+    from oracle import sihc_model_oracle as MO
+    meta, t, model = build_from_golden()
+    x, tt, y = golden_inputs(meta, t)
+    ref = copy.deepcopy(model)
+    model = model.cuda()
+    auto = torch.autocast("cuda", dtype=torch.bfloat16, enabled=dtype == torch.bfloat16)
+    with torch.no_grad(), auto:
+        factored = model(x.cuda(), tt.cuda(), y.cuda())
+        model.inference_schedule = "literal"
+        literal = model(x.cuda(), tt.cuda(), y.cuda())
+    with torch.no_grad(), torch.autocast("cpu", dtype=torch.bfloat16, enabled=dtype == torch.bfloat16):
+        expect = MO.literal_forward(ref, x, tt, y)
+    atol, rtol = (3e-5, 3e-4) if dtype == torch.float32 else (0.025, 0.03)
+    torch.testing.assert_close(literal.float().cpu(), expect.float(), atol=atol, rtol=rtol)
+    torch.testing.assert_close(literal.float(), factored.float(), atol=atol, rtol=rtol)
+    if dtype == torch.float32:
+        torch.testing.assert_close(literal.flatten()[::meta["stride"]].cpu(), t["out_sample"], atol=3e-5, rtol=3e-4)
+    with pytest.raises(RuntimeError):
+        with torch.enable_grad():
+            model.run_literal(torch.zeros(1, 32, 32, 32, device="cuda"), torch.zeros(1, 32, device="cuda"))

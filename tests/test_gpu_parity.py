@@ -336,3 +336,26 @@ def test_single_event_adjoints_register_and_ring_variants(R, stages, slots, dtyp
     close(got["ddz"], torch.stack(oddz), dtype, "ddz")
     close(got["dalpha"], oda.to(dtype), dtype, "dalpha")
     close(got["dbeta"], odb.to(dtype), dtype, "dbeta")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("slots,b,g,c", [(4, 3, 7, 67), (4, 4, 16, 768), (2, 2, 5, 64), (8, 2, 6, 128), (16, 2, 4, 64)])
+def test_fused_write_then_read_step_is_the_unfused_pair(R, slots, b, g, c, dtype):
+    """sihc_write_read == write_torch followed by read_torch, including the rounding of the carrier
+    between the two (so bf16 results are bit-identical to the unfused oracle pair)."""
+    torch.manual_seed(40 + slots + c)
+    kh, kw = O.cell_shape(slots)
+    x = torch.randn(b, g * kh, g * kw, c).to(dtype)
+    dz = torch.randn(b, g * g, c).to(dtype)
+    beta = (1.0 + 0.05 * torch.randn(c, slots)).to(dtype)
+    alpha = (1.0 / slots + 0.05 * torch.randn(c, slots)).to(dtype)
+    y, z = R.sihc_write_read(x.to(DEV), dz.to(DEV), beta.to(DEV), alpha.to(DEV))
+    oy = O.write(x, [dz], [beta])
+    oz = O.read(oy, alpha)
+    close(y, oy, dtype, "carrier")
+    close(z, oz, dtype, "next read")
+    # and it agrees with this library's own separate write + read
+    y2 = R.sihc_write(x.to(DEV), dz.to(DEV), beta.to(DEV))
+    z2 = R.sihc_read(y2, alpha.to(DEV))
+    assert torch.equal(y, y2)
+    close(z, z2, dtype, "fused vs separate")

@@ -468,7 +468,10 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         net = torch.compile(model, fullgraph=True) if compile_model else model
         if world > 1:
             from torch.nn.parallel import DistributedDataParallel as DDP
-            net = DDP(net, device_ids=[local_rank], gradient_as_bucket_view=True)
+            # 512 MB buckets: the compiled backward is one autograd node, so every gradient becomes ready at its
+            # end and the default 25 MB buckets turn into ~110 back-to-back latency-bound all-reduces
+            # (measured on 2 x B200: 85.4 ms per step with 25 MB buckets, 66.7 ms with 512 MB, 62.0 ms on one GPU)
+            net = DDP(net, device_ids=[local_rank], gradient_as_bucket_view=True, bucket_cap_mb=512)
         opt = torch.optim.AdamW(model.parameters(), lr=2e-4, betas=(0.9, 0.95), weight_decay=0.0, fused=True)
         x_host = torch.randn(batch, 3, 256, 256, generator=gen).pin_memory()
         y = torch.randint(0, 1000, (batch,), device=device)

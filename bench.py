@@ -200,13 +200,14 @@ def run_e2e(args, batch, grid, slots, channels, dtype, device, steps):
 
     The per-GPU batch is streamed in chunks: each chunk's inputs are copied from
     pinned host memory, the four passes run through ``sihc_read`` / ``sihc_write``
-    and autograd, and every result is copied back to pinned host memory.  Two
-    CUDA streams overlap the copies of one chunk with the kernels of the other.
+    and autograd, and every result is copied back to pinned host memory.  Three
+    CUDA streams (copy-in, kernels, copy-out) keep both PCIe directions and the
+    GPU busy at once.
     """
     import residual_stream_burden_b200 as R
     torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False)   # side streams are intended here
     kh, kw = CELLS[slots]
-    chunk = min(batch, 256)
+    chunk = min(batch, 128)
     nchunks = (batch + chunk - 1) // chunk
     gen = torch.Generator().manual_seed(1)
     ibits = torch.int16 if dtype == torch.bfloat16 else torch.int32
@@ -218,45 +219,62 @@ def run_e2e(args, batch, grid, slots, channels, dtype, device, steps):
         return t
 
     carrier, work = (chunk, grid * kh, grid * kw, channels), (chunk, grid * grid, channels)
+    NB = 3                                                         # chunks in flight: copy-in / compute / copy-out
     h_in = dict(x=host(*carrier), dz=host(*work), gz=host(*work), gy=host(*carrier))
-    h_out = [dict(z=host(*work), y=host(*carrier), dx=host(*carrier), ddz=host(*work)) for _ in range(2)]
+    h_out = [dict(z=host(*work), y=host(*carrier), dx=host(*carrier), ddz=host(*work)) for _ in range(NB)]
     h_dw = torch.empty(2, channels, slots, dtype=dtype).pin_memory()
     alpha = torch.full((channels, slots), 1.0 / slots, device=device, dtype=dtype).requires_grad_()
     beta = torch.full((channels, slots), 1.0, device=device, dtype=dtype).requires_grad_()
-    streams = [torch.cuda.Stream(device=device) for _ in range(2)]
-    d_in = [{k: torch.empty_like(v, device=device) for k, v in h_in.items()} for _ in range(2)]
-    sums = [torch.zeros(2, channels, slots, device=device, dtype=torch.float32) for _ in range(2)]
+    s_in, s_cmp, s_out = (torch.cuda.Stream(device=device) for _ in range(3))
+    d_in = [{k: torch.empty_like(v, device=device) for k, v in h_in.items()} for _ in range(NB)]
+    sums = torch.zeros(2, channels, slots, device=device, dtype=torch.float32)
     esize = h_in["x"].element_size()
     h2d = sum(v.numel() for v in h_in.values()) * esize * nchunks
     d2h = (sum(v.numel() for v in h_out[0].values()) * nchunks + h_dw.numel()) * esize
 
     def step():
+        # three engines busy at once: H2D of chunk k+1, kernels of chunk k, D2H of chunk k-1
         main_stream = torch.cuda.current_stream()
-        for si, s in enumerate(streams):
+        for s in (s_in, s_cmp, s_out):
             s.wait_stream(main_stream)
-            with torch.cuda.stream(s):
-                sums[si].zero_()
+        with torch.cuda.stream(s_cmp):
+            sums.zero_()
+        in_free = [None] * NB       # event: kernels have consumed input buffer b
+        out_free = [None] * NB      # event: D2H of host buffer b has finished
         for ci in range(nchunks):
-            si = ci % 2
-            buf, out = d_in[si], h_out[si]
-            with torch.cuda.stream(streams[si]):
+            b = ci % NB
+            buf, out = d_in[b], h_out[b]
+            with torch.cuda.stream(s_in):
+                if in_free[b] is not None:
+                    s_in.wait_event(in_free[b])
                 for k in h_in:
                     buf[k].copy_(h_in[k], non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ev_in)
                 x = buf["x"].detach().requires_grad_()
                 dz = buf["dz"].detach().requires_grad_()
                 z = R.sihc_read(x, alpha)
                 y = R.sihc_write(x, dz, beta)
                 dx, da = torch.autograd.grad(z, (x, alpha), buf["gz"])
                 ddz, db = torch.autograd.grad(y, (dz, beta), buf["gy"])
-                out["z"].copy_(z, non_blocking=True)
-                out["y"].copy_(y, non_blocking=True)
-                out["dx"].copy_(dx, non_blocking=True)
-                out["ddz"].copy_(ddz, non_blocking=True)
-                sums[si][0].add_(da)
-                sums[si][1].add_(db)
-        for s in streams:
+                sums[0].add_(da)
+                sums[1].add_(db)
+                in_free[b] = torch.cuda.Event()
+                in_free[b].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(in_free[b])
+                if out_free[b] is not None:
+                    s_out.wait_event(out_free[b])
+                for name, t in (("z", z), ("y", y), ("dx", dx), ("ddz", ddz)):
+                    t.record_stream(s_out)
+                    out[name].copy_(t, non_blocking=True)
+                out_free[b] = torch.cuda.Event()
+                out_free[b].record(s_out)
+        for s in (s_in, s_cmp, s_out):
             main_stream.wait_stream(s)
-        h_dw.copy_((sums[0] + sums[1]).to(dtype), non_blocking=True)
+        h_dw.copy_(sums.to(dtype), non_blocking=True)
 
     step()
     torch.cuda.synchronize()
@@ -635,14 +653,20 @@ def main():
             dist.all_reduce(path.wgrads)
             path.wgrads.div_(world)
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
+    # The clock sampler (nvidia-smi, 100 ms period) needs a few hundred ms to deliver its first line, longer
+    # than the timed region itself, so it is started first and the same step keeps running as warm-up until it
+    # has reported at least three samples under load (bounded); its record covers warm-up + timed steps.
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    warm_done, t_warm = 0, time.perf_counter()
+    while warm_done < max(args.warmup, 3) or (rank == 0 and world == 1 and sampler.proc is not None
+                                               and len(sampler.samples) < 3 and time.perf_counter() - t_warm < 3.0):
+        step()
+        torch.cuda.synchronize()
+        warm_done += 1
+    if world > 1:
+        dist.barrier()
     per_kernel = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(4)]
                   for _ in range(args.steps)]
     launches0 = _lib.launch_count()
@@ -718,7 +742,7 @@ def main():
 
     if rank == 0:
         line = {"metric": "sihc_read_write_fwd_bwd_bandwidth", "value": round(value, 1), "unit": "GB/s",
-                "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "n_gpus": world, "steps": args.steps, "warmup": warm_done,
                 "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "config": config,
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),

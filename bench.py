@@ -353,7 +353,7 @@ def run_sweep(args, device, rank, world):
 
 # ------------------------------------------------------------------------------------------ stage ops
 def run_stage_ops(args, device, steps, warmup):
-    """The multi-event stage operators one by one on SiHC-B's stage shapes (BASELINE config 2: batch 256,
+    """The multi-event stage operators one by one on SiHC-B's stage shapes (the SiHC-B forward configuration: batch 256,
     256 tokens, n=4, width 768, E=24 events): read(E), triangular(E-1), write(E) and their backward calls.
     GB/s are algorithmic bytes (read S+E, write 2S+E, triangular J+2, read bwd 2(S+E) as two kernels,
     write bwd 2(S+E), triangular bwd 2J+1) over the CUDA-event time of the C ABI call."""

@@ -158,7 +158,7 @@ def main(reference_root: str) -> None:
 
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     f32, bf16 = torch.float32, torch.bfloat16
-    # BASELINE config 1: batch 4, 256 tokens, n=4, width 768, fp32, seed 0.
+    # The standalone-op configuration: batch 4, 256 tokens, n=4, width 768, fp32, seed 0.
     op_case("cfg1_fp32", fc, seed=0, b=4, g=16, slots=4, c=768, events=1, dtype=f32,
             scale_a=0.02, mean_a=0.25, scale_b=0.02, mean_b=1.0, sample_stride=251)
     op_case("cfg1_bf16", fc, seed=0, b=4, g=16, slots=4, c=768, events=1, dtype=bf16,

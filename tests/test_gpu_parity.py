@@ -59,7 +59,7 @@ def test_golden_op_cases(R, case, tag):
 
 @pytest.mark.parametrize("tag", ["fp32", "bf16"])
 def test_golden_config1_seed0(R, tag):
-    """BASELINE config 1: batch 4, 256 tokens, n=4, width 768, seed 0, all outputs and gradients."""
+    """The standalone-op configuration: batch 4, 256 tokens, n=4, width 768, seed 0, all outputs and gradients."""
     meta, t = load_golden(f"cfg1_{tag}")
     dtype = getattr(torch, meta["dtype"])
     stride = meta["sample_stride"]

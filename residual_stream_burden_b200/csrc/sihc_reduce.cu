@@ -12,7 +12,7 @@ namespace sihc {
 
 struct WGradParams { const void* x; ConstPtrs z; float* partial; int E; Tiling t; };
 struct TriFwdParams { const void* base; ConstPtrs dz; const void* gamma; void* out; int J; Tiling t; };
-struct TriBwdParams { const void* grad; ConstPtrs dz; const void* gamma; MutPtrs ddz; int has_ddz; float* partial; int J; Tiling t; };
+struct TriBwdParams { const void* grad; ConstPtrs dz; const void* gamma; MutPtrs ddz; int has_ddz; float* partial; int J; int chunk; Tiling t; };
 
 
 // Events handled per pass over the carrier by the stage weight-gradient kernel.
@@ -201,7 +201,8 @@ __global__ void __launch_bounds__(kMaxThreads) tri_bwd_kernel(const __grid_const
     __shared__ float red[kMaxThreads * V];
     const Tiling& t = p.t;
     const Lane ln = make_lane<V>(t);
-    const int e0 = blockIdx.z * JC;
+    const int e0 = blockIdx.z * p.chunk;          // p.chunk <= JC events per z-slice, balanced across slices
+    const int e1 = e0 + p.chunk < p.J ? e0 + p.chunk : p.J;
     const T* __restrict__ grad = static_cast<const T*>(p.grad) + ln.c0;
     float acc[JC][V];
 #pragma unroll
@@ -231,7 +232,7 @@ __global__ void __launch_bounds__(kMaxThreads) tri_bwd_kernel(const __grid_const
 #pragma unroll
             for (int j = 0; j < JC; ++j) {
                 const int l = e0 + j;
-                const bool have = l < p.J && p.partial != nullptr;
+                const bool have = l < e1 && p.partial != nullptr;
                 const T* __restrict__ dz = have ? static_cast<const T*>(p.dz.p[l]) + ln.c0 : nullptr;
 #pragma unroll
                 for (int i = 0; i < TT; ++i)
@@ -240,7 +241,7 @@ __global__ void __launch_bounds__(kMaxThreads) tri_bwd_kernel(const __grid_const
 #pragma unroll
             for (int j = 0; j < JC; ++j) {
                 const int l = e0 + j;
-                if (l < p.J) {
+                if (l < e1) {
 #pragma unroll
                     for (int i = 0; i < TT; ++i) {
                         float d[V];
@@ -268,7 +269,7 @@ __global__ void __launch_bounds__(kMaxThreads) tri_bwd_kernel(const __grid_const
     }
     if (p.partial != nullptr) {
         float* dst = p.partial + (static_cast<size_t>(blockIdx.x) * p.J + e0) * t.C;
-        const int live = p.J - e0 < JC ? p.J - e0 : JC;
+        const int live = e1 - e0;
 #pragma unroll
         for (int a = 0; a < JC; ++a) {
             float one[1][V];
@@ -355,6 +356,7 @@ cudaError_t launch_tri_bwd(const Problem& pb, const void* grad, const void* cons
             if constexpr (V > 16 / int(sizeof(T))) return cudaErrorInvalidValue;
             else {
                 const uint32_t gz = static_cast<uint32_t>((pb.E + kTriChunk - 1) / kTriChunk);
+                p.chunk = (pb.E + static_cast<int>(gz) - 1) / static_cast<int>(gz);     // e.g. 12 events -> 2 slices of 6
                 return launch_persistent(tri_bwd_kernel<T, W, V, TT>, p, pb, V, TT, 512, gz, partial != nullptr, blocks);
             }
         });

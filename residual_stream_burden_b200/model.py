@@ -372,10 +372,12 @@ def velocity_training_batch(x: Tensor, generator: torch.Generator | None = None)
 def cfg_velocity(model, z, t, labels, *, num_classes, cfg_scale, interval):
     """Classifier-free guidance on a guidance interval (reference: ``cfg_velocity``, sihc/sampling.py:20-29):
     two separate forwards (conditional, null label) whenever ``cfg_scale != 1``."""
-    v_cond = model(z, t.flatten(), labels)
+    # clone(): a model compiled with CUDA graphs may reuse its output buffer on the next call, and both
+    # evaluations must be alive at once (same precaution as the reference, sihc/sampling.py:8-11)
+    v_cond = model(z, t.flatten(), labels).clone()
     if cfg_scale == 1.0:
         return v_cond
-    v_null = model(z, t.flatten(), torch.full_like(labels, num_classes))
+    v_null = model(z, t.flatten(), torch.full_like(labels, num_classes)).clone()
     low, high = interval
     mask = (t < high) & ((low == 0) | (t > low))
     scale = torch.where(mask, torch.full_like(t, cfg_scale), torch.ones_like(t))

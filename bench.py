@@ -466,6 +466,10 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         model = sihc_b().to(device).eval()
         model.open_gates()
         model.inference_schedule = "literal"        # n = 4: fused write+read steps move fewer bytes than the factored stage
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):     # one eager pass: counts this
+            model(torch.randn(2, 3, 256, 256, device=device), torch.rand(2, device=device),  # library's launches
+                  torch.zeros(2, dtype=torch.long, device=device))              # (graph replays are not counted)
+        per_step_launches = _lib.launch_count() - launches0
         net = torch.compile(model, fullgraph=True, mode="reduce-overhead") if compile_model else model
         x_host = torch.randn(batch, 3, 256, 256, generator=gen).pin_memory()
         t = torch.rand(batch, device=device)
@@ -484,6 +488,11 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         batch = 32
         model = sihc_xl().to(device)
         model.open_gates()
+        with torch.autocast("cuda", dtype=torch.bfloat16):                      # one eager forward+backward: counts
+            model(torch.randn(2, 3, 256, 256, device=device), torch.rand(2, device=device),   # this library's launches
+                  torch.zeros(2, dtype=torch.long, device=device)).float().mean().backward()
+        model.zero_grad(set_to_none=True)
+        per_step_launches = _lib.launch_count() - launches0
         net = torch.compile(model, fullgraph=True, mode="reduce-overhead") if compile_model else model
         if world > 1:
             from torch.nn.parallel import DistributedDataParallel as DDP
@@ -514,6 +523,10 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         model = sihc_xl().to(device).eval()
         model.open_gates()
         model.inference_schedule = "literal"
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            model(torch.randn(2, 3, 256, 256, device=device), torch.rand(2, device=device),
+                  torch.zeros(2, dtype=torch.long, device=device))
+        per_step_launches = (_lib.launch_count() - launches0) * 2 * (2 * sample_steps - 1)   # two forwards per guided evaluation
         net = torch.compile(model, fullgraph=True, mode="reduce-overhead") if compile_model else model
         y = torch.randint(0, 1000, (batch,), device=device)
 
@@ -524,10 +537,9 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
 
         ms = time_device(step, steps, warmup, world, device)
         name = f"SiHC-XL Heun sampling, {sample_steps} steps, CFG 2.4 on [0.1,0.9], batch 256 per GPU, bf16 autocast, literal fused write+read schedule"
-    launches = _lib.launch_count() - launches0
     name += ", torch.compile (CUDA graphs) around the torch sublayers" if compile_model else ", eager"
     res = {"workload": name, "img_per_s": round(world * batch / (ms * 1e-3), 2), "ms_per_step": round(ms, 3),
-           "global_batch": world * batch, "routing_launches_per_step": launches // max(1, steps + warmup),
+           "global_batch": world * batch, "routing_launches_per_step": per_step_launches,
            "peak_mem_gb": round(torch.cuda.max_memory_allocated(device) / 2**30, 2)}
     del model
     torch.cuda.empty_cache()

@@ -359,3 +359,35 @@ def test_fused_write_then_read_step_is_the_unfused_pair(R, slots, b, g, c, dtype
     z2 = R.sihc_read(y2, alpha.to(DEV))
     assert torch.equal(y, y2)
     close(z, z2, dtype, "fused vs separate")
+
+
+@pytest.mark.parametrize("slots,c,events", [(4, 4104, 1), (8, 2056, 1), (4, 4104, 3), (2, 4100, 2)])
+def test_channel_counts_wider_than_one_block(R, slots, c, events):
+    """More channel vectors than a block has lanes: the channel dimension is tiled over blockIdx.y,
+    with a partly filled last tile (and, for 4100 channels in bf16, the scalar path)."""
+    dtype = torch.bfloat16
+    torch.manual_seed(c + slots)
+    kh, kw = O.cell_shape(slots)
+    b, g = 2, 5
+    x = torch.randn(b, g * kh, g * kw, c).to(dtype)
+    alpha = (1.0 / slots + 0.05 * torch.randn(events, c, slots)).to(dtype)
+    beta = (1.0 + 0.05 * torch.randn(events, c, slots)).to(dtype)
+    dz = [torch.randn(b, g * g, c).to(dtype) for _ in range(events)]
+    gz = [torch.randn(b, g * g, c).to(dtype) for _ in range(events)]
+    gy = torch.randn(b, g * kh, g * kw, c).to(dtype)
+    got = run_all(R, x, alpha, beta, dz, gz, gy)
+    close(got["z"], torch.stack(O.multi_read(x, alpha)), dtype, "z")
+    close(got["y"], O.write(x, dz, beta), dtype, "y")
+    odx, oda = O.read_backward(x, gz, alpha, acc=torch.float64)
+    oddz, odb = O.write_backward(gy, dz, beta, acc=torch.float64)
+    close(got["dx_read"], odx, dtype, "dx_read")
+    close(got["ddz"], torch.stack(oddz), dtype, "ddz")
+    close(got["dalpha"], oda.to(dtype), dtype, "dalpha")
+    close(got["dbeta"], odb.to(dtype), dtype, "dbeta")
+    base = torch.randn(b, g * g, c).to(dtype)
+    gamma = torch.randn(events, c) * 0.05
+    out = R.sublayer_triangular(base.to(DEV), [t.to(DEV) for t in dz], gamma.to(DEV))
+    close(out, O.triangular(base, dz, gamma), dtype, "triangular")
+    y2, z2 = R.sihc_write_read(x.to(DEV), dz[0].to(DEV), beta[0].to(DEV), alpha[0].to(DEV))
+    close(y2, O.write(x, [dz[0]], [beta[0]]), dtype, "write_read y")
+    close(z2, O.read(O.write(x, [dz[0]], [beta[0]]), alpha[0]), dtype, "write_read z")

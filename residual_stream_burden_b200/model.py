@@ -1,6 +1,7 @@
-"""Sublayer-wise SiHC denoiser: the caller of the routing operators.
+"""SiHC denoisers: the callers of the routing operators.
 
-A self-contained mirror of the reference's sublayer-wise model
+A self-contained mirror of the reference's sublayer-wise and block-wise models, with or without class-prefix
+context tokens
 (``SublayerSiHCModel``, sihc/models/sihc/sublayer.py:30-72, on top of
 ``_SiHCBase``, sihc/models/sihc/model.py:186-513, and the blocks of
 sihc/models/sihc/components.py).  Parameter names, shapes and initialisation
@@ -56,7 +57,7 @@ class AxialRope(nn.Module):
     (reference: ``VisionRotaryEmbeddingFast``, sihc/models/sihc/components.py:39-76).
     """
 
-    def __init__(self, half_head_dim: int, grid: int, theta: float = 10000.0):
+    def __init__(self, half_head_dim: int, grid: int, theta: float = 10000.0, prefix_tokens: int = 0):
         super().__init__()
         inv = 1.0 / (theta ** (torch.arange(0, half_head_dim, 2).float()[: half_head_dim // 2] / half_head_dim))
         ang = torch.arange(grid).float()[:, None] * inv[None, :]
@@ -64,8 +65,12 @@ class AxialRope(nn.Module):
         rows = ang[:, None, :].expand(grid, grid, -1)
         cols = ang[None, :, :].expand(grid, grid, -1)
         full = torch.cat([rows, cols], dim=-1).reshape(grid * grid, -1)          # [tokens, head_dim]
-        self.register_buffer("freqs_cos", full.cos(), persistent=False)
-        self.register_buffer("freqs_sin", full.sin(), persistent=False)
+        cos, sin = full.cos(), full.sin()
+        if prefix_tokens:            # class-prefix tokens carry no position: identity rotation
+            cos = torch.cat([torch.ones(prefix_tokens, cos.shape[-1]), cos], dim=0)
+            sin = torch.cat([torch.zeros(prefix_tokens, sin.shape[-1]), sin], dim=0)
+        self.register_buffer("freqs_cos", cos, persistent=False)
+        self.register_buffer("freqs_sin", sin, persistent=False)
 
     def forward(self, x: Tensor) -> Tensor:
         cos = self.freqs_cos.to(x.device, x.dtype)
@@ -171,6 +176,12 @@ class Branch(nn.Module):
         shift, scale, gate = mod[3], mod[4], mod[5]
         return gate.unsqueeze(1) * self.mlp(_modulate(self.norm2(z), shift, scale))
 
+    def forward(self, z: Tensor, cond: Tensor, rope: AxialRope) -> Tensor:
+        """Whole-block update (one block-wise connection event): attention, then MLP on ``z + dz_attn``."""
+        mod = self.conditioning(cond)
+        dz_attn = self.attention_update(z, mod, rope)
+        return dz_attn + self.mlp_update(z + dz_attn, mod)
+
 
 class Connection(nn.Module):
     """Feature-wise read/write maps of one connection event: ``read_weight``, ``write_weight`` ``[C, S]``
@@ -196,6 +207,15 @@ class SublayerBlock(nn.Module):
         self.branch = Branch(hidden, heads, mlp_ratio)
 
 
+class BlockwiseBlock(nn.Module):
+    """One connection event per block (reference: ``SiHCBlock``, sihc/models/sihc/model.py:156-183)."""
+
+    def __init__(self, hidden: int, heads: int, slots: int, mlp_ratio: float):
+        super().__init__()
+        self.connection = Connection(hidden, slots)
+        self.branch = Branch(hidden, heads, mlp_ratio)
+
+
 class FinalLayer(nn.Module):
     def __init__(self, hidden: int, patch: int, out_channels: int):
         super().__init__()
@@ -208,17 +228,26 @@ class FinalLayer(nn.Module):
         return self.linear(_modulate(self.norm_final(x), shift, scale))
 
 
-class SublayerSiHC(nn.Module):
-    """SiHC with separate connection events around attention and MLP, fused per stage.
+class SiHC(nn.Module):
+    """SiHC denoiser with the residual carrier routed by the fused CUDA operators, one fused stage at a time.
 
-    ``stage_sizes`` counts blocks per stage (each 1..12, i.e. at most 24 events).
-    ``patch_size`` 8 gives n = 4 residual streams per workspace token, 4 gives n = 16.
+    ``frequency="sublayer"``: separate connection events around attention and MLP (2 per block; reference
+    ``SublayerSiHCModel``); ``"block"``: one event per block (reference ``SiHCModel`` with the tuple
+    backend, sihc/models/sihc/model.py:430-473).  ``stage_sizes`` counts blocks per stage (at most 24
+    events per stage).  ``patch_size`` 8 gives n = 4 residual streams per workspace token, 4 gives n = 16.
+    ``in_context_len > 0`` adds persistent class-prefix tokens that join the workspace sequence from block
+    ``in_context_start`` on, have ordinary residual updates and never enter the spatial routing (reference
+    ``SiHCInContextModel`` / ``SublayerSiHCInContextModel``, sihc/models/sihc/model.py:562-639,
+    sihc/models/sihc/sublayer.py:75-122).
     """
 
     def __init__(self, input_size: int = 256, patch_size: int = 8, in_channels: int = 3, hidden_size: int = 768,
                  depth: int = 12, num_heads: int = 12, mlp_ratio: float = 4.0, num_classes: int = 1000,
-                 workspace_grid: int = 16, stage_sizes: Sequence[int] | None = None, fused_stage_size: int = 12):
+                 workspace_grid: int = 16, stage_sizes: Sequence[int] | None = None, fused_stage_size: int = 12,
+                 frequency: str = "sublayer", in_context_len: int = 0, in_context_start: int = 0):
         super().__init__()
+        if frequency not in ("sublayer", "block"):
+            raise ValueError("frequency must be 'sublayer' or 'block'")
         high = input_size // patch_size
         if input_size % patch_size or high % workspace_grid:
             raise ValueError("patch size must give a high-resolution grid divisible by the workspace grid")
@@ -226,17 +255,26 @@ class SublayerSiHC(nn.Module):
         if k * k not in ops.CELLS or ops.CELLS[k * k] != (k, k):
             raise ValueError(f"unsupported cell {k}x{k}")
         stages = tuple(int(s) for s in stage_sizes) if stage_sizes is not None else (fused_stage_size,) * (depth // fused_stage_size)
-        if sum(stages) != depth or any(not 1 <= s <= 12 for s in stages):
-            raise ValueError(f"stage sizes {stages} must be in 1..12 and sum to depth {depth}")
+        per_block = 2 if frequency == "sublayer" else 1
+        if sum(stages) != depth or any(not 1 <= s * per_block <= 24 for s in stages):
+            raise ValueError(f"stage sizes {stages} must give 1..24 events each and sum to depth {depth}")
+        if in_context_len < 0 or (in_context_len and not 0 <= in_context_start < depth):
+            raise ValueError("in_context_len must be >= 0 and in_context_start inside the depth")
         self.input_size, self.patch_size, self.in_channels, self.out_channels = input_size, patch_size, in_channels, in_channels
         self.hidden_size, self.depth, self.num_heads, self.num_classes = hidden_size, depth, num_heads, num_classes
         self.workspace_grid, self.high_grid, self.slots, self.stage_sizes = workspace_grid, high, k * k, stages
+        self.frequency, self.in_context_len, self.in_context_start = frequency, int(in_context_len), int(in_context_start)
         self.t_embedder = TimestepEmbedder(hidden_size)
         self.y_embedder = LabelEmbedder(num_classes, hidden_size)
         self.x_embedder = PatchStem(input_size, patch_size, in_channels, hidden_size)
-        self.workspace_rope = AxialRope(hidden_size // num_heads // 2, workspace_grid)
-        self.blocks = nn.ModuleList(SublayerBlock(hidden_size, num_heads, k * k, mlp_ratio) for _ in range(depth))
+        half_head = hidden_size // num_heads // 2
+        self.workspace_rope = AxialRope(half_head, workspace_grid)
+        block_cls = SublayerBlock if frequency == "sublayer" else BlockwiseBlock
+        self.blocks = nn.ModuleList(block_cls(hidden_size, num_heads, k * k, mlp_ratio) for _ in range(depth))
         self.final_layer = FinalLayer(hidden_size, patch_size, in_channels)
+        if self.in_context_len:
+            self.in_context_posemb = nn.Parameter(torch.empty(1, self.in_context_len, hidden_size))
+            self.workspace_rope_incontext = AxialRope(half_head, workspace_grid, prefix_tokens=self.in_context_len)
         # "factored": one read, triangular accumulation, one write per stage (training and default).
         # "literal": write event i and read event i+1 in one pass over the carrier, no triangular step;
         # forward-only, fewer bytes than the factored stage when n <= 4 (10 vs ~16 elements per event at E=24).
@@ -262,6 +300,11 @@ class SublayerSiHC(nn.Module):
         nn.init.zeros_(self.final_layer.adaLN_modulation[-1].bias)
         nn.init.zeros_(self.final_layer.linear.weight)
         nn.init.zeros_(self.final_layer.linear.bias)
+        if self.in_context_len:
+            nn.init.normal_(self.in_context_posemb, std=0.02)
+
+    def connections(self, block) -> list:
+        return [block.attention_connection, block.mlp_connection] if self.frequency == "sublayer" else [block.connection]
 
     @torch.no_grad()
     def open_gates(self, std: float = 0.01) -> None:
@@ -271,7 +314,7 @@ class SublayerSiHC(nn.Module):
         for block in self.blocks:
             block.branch.adaLN_modulation[-1].weight.normal_(std=std)
             block.branch.adaLN_modulation[-1].bias.normal_(std=3 * std)
-            for conn in (block.attention_connection, block.mlp_connection):
+            for conn in self.connections(block):
                 conn.read_weight.add_(torch.randn_like(conn.read_weight) * std)
                 conn.write_weight.add_(torch.randn_like(conn.write_weight) * 2 * std)
         self.final_layer.linear.weight.normal_(std=3 * std)
@@ -282,60 +325,103 @@ class SublayerSiHC(nn.Module):
         return x.reshape(b, h, h, p, p, c).permute(0, 5, 1, 3, 2, 4).reshape(b, c, h * p, h * p)
 
     # ---- the hot path's caller -----------------------------------------------------------------
-    def run_stage(self, x0: Tensor, cond: Tensor, blocks: Sequence[SublayerBlock]) -> Tensor:
-        """One fused stage (reference: ``_run_fused_schedule_stage``, sihc/models/sihc/sublayer.py:52-72)."""
-        conns = [c for block in blocks for c in (block.attention_connection, block.mlp_connection)]
-        alpha = torch.stack([c.alpha(dtype=x0.dtype) for c in conns]).contiguous()
-        beta = torch.stack([c.beta(dtype=x0.dtype) for c in conns]).contiguous()
+    def stage_events(self, blocks: Sequence[nn.Module], cond: Tensor, stage_start: int) -> list:
+        """The connection events of a stage, in order: ``(connection, update, uses_context)`` where
+        ``update(seq, rope)`` is the gated sublayer (or whole-block) update of a token sequence."""
+        events = []
+        for i, block in enumerate(blocks):
+            ctx = bool(self.in_context_len) and stage_start + i >= self.in_context_start
+            if self.frequency == "sublayer":
+                mod = block.branch.conditioning(cond)
+                events.append((block.attention_connection,
+                               lambda seq, rope, b=block, m=mod: b.branch.attention_update(seq, m, rope), ctx))
+                events.append((block.mlp_connection,
+                               lambda seq, rope, b=block, m=mod: b.branch.mlp_update(seq, m), ctx))
+            else:
+                events.append((block.connection, lambda seq, rope, b=block: b.branch(seq, cond, rope), ctx))
+        return events
+
+    def apply_update(self, update, z: Tensor, context: Tensor | None, uses_context: bool):
+        """Run one event's sublayer on ``z`` (with the class-prefix tokens in front when they are active);
+        returns the packed spatial update and the new prefix tokens."""
+        if uses_context:
+            dseq = update(torch.cat((context, z), dim=1), self.workspace_rope_incontext)
+            n = self.in_context_len
+            # dropping the prefix gives a batch-strided view: the routing operators need it packed
+            return dseq[:, n:].contiguous(), context + dseq[:, :n]
+        return update(z, self.workspace_rope).contiguous(), context
+
+    def run_stage(self, x0: Tensor, cond: Tensor, blocks: Sequence[nn.Module], stage_start: int = 0,
+                  context: Tensor | None = None):
+        """One fused stage (reference: ``_run_fused_schedule_stage``, sihc/models/sihc/sublayer.py:52-72, :84-122;
+        block-wise sihc/models/sihc/model.py:430-473, :588-639).  Returns ``(carrier, context)``."""
+        events = self.stage_events(blocks, cond, stage_start)
+        alpha = torch.stack([c.alpha(dtype=x0.dtype) for c, _, _ in events]).contiguous()
+        beta = torch.stack([c.beta(dtype=x0.dtype) for c, _, _ in events]).contiguous()
         base = ops.sublayer_read(x0, alpha)
         gamma = (alpha[:, None] * beta[None, :]).sum(dim=-1)
         updates: list[Tensor] = []
-        for i, block in enumerate(blocks):
-            mod = block.branch.conditioning(cond)
-            z = base[2 * i]
-            if updates:
-                z = ops.sublayer_triangular(z, updates, gamma[2 * i, :2 * i].contiguous())
-            updates.append(block.branch.attention_update(z, mod, self.workspace_rope).contiguous())
-            z = ops.sublayer_triangular(base[2 * i + 1], updates, gamma[2 * i + 1, :2 * i + 1].contiguous())
-            updates.append(block.branch.mlp_update(z, mod).contiguous())
-        return ops.sublayer_write(x0, updates, beta)
+        for e, (_, update, uses_context) in enumerate(events):
+            z = base[e] if e == 0 else ops.sublayer_triangular(base[e], updates, gamma[e, :e].contiguous())
+            dz, context = self.apply_update(update, z, context, uses_context)
+            updates.append(dz)
+        return ops.sublayer_write(x0, updates, beta), context
 
-    def run_literal(self, carrier: Tensor, cond: Tensor) -> Tensor:
+    def run_literal(self, carrier: Tensor, cond: Tensor, context: Tensor | None = None) -> Tensor:
         """All events with the literal recurrence (reference definition: ``literal_forward``,
         research/tests/test_sublayer_kernels.py:216-226), each write fused with the next event's read."""
         if torch.is_grad_enabled():
             raise RuntimeError("the literal schedule is forward-only: call it under torch.no_grad()")
-        events = [(block, conn, kind) for block in self.blocks
-                  for conn, kind in ((block.attention_connection, "attn"), (block.mlp_connection, "mlp"))]
+        events, start = [], 0
+        for size in self.stage_sizes:
+            events += self.stage_events(self.blocks[start:start + size], cond, start)
+            start += size
         dtype = carrier.dtype
-        z = ops.sihc_read(carrier, events[0][1].alpha(dtype).contiguous())
-        mod = None
-        for i, (block, conn, kind) in enumerate(events):
-            if kind == "attn":
-                mod = block.branch.conditioning(cond)
-                dz = block.branch.attention_update(z, mod, self.workspace_rope).contiguous()
-            else:
-                dz = block.branch.mlp_update(z, mod).contiguous()
+        z = ops.sihc_read(carrier, events[0][0].alpha(dtype).contiguous())
+        for i, (conn, update, uses_context) in enumerate(events):
+            dz, context = self.apply_update(update, z, context, uses_context)
             if i + 1 < len(events):
                 carrier, z = ops.sihc_write_read(carrier, dz, conn.beta(dtype).contiguous(),
-                                                 events[i + 1][1].alpha(dtype).contiguous())
+                                                 events[i + 1][0].alpha(dtype).contiguous())
             else:
                 carrier = ops.sihc_write(carrier, dz, conn.beta(dtype).contiguous())
         return carrier
 
+    def initial_context(self, y_emb: Tensor, dtype) -> Tensor | None:
+        if not self.in_context_len:
+            return None
+        return (y_emb.unsqueeze(1).expand(-1, self.in_context_len, -1) + self.in_context_posemb).to(dtype=dtype)
+
     def forward(self, x: Tensor, t: Tensor, y: Tensor) -> Tensor:
-        cond = self.t_embedder(t) + self.y_embedder(y)
+        y_emb = self.y_embedder(y)
+        cond = self.t_embedder(t) + y_emb
         carrier = self.x_embedder(x)
+        context = self.initial_context(y_emb, carrier.dtype)
         if self.inference_schedule == "literal" and not torch.is_grad_enabled():
-            carrier = self.run_literal(carrier, cond)
-            b, hh, ww, c = carrier.shape
-            return self.unpatchify(self.final_layer(carrier.reshape(b, hh * ww, c), cond))
-        start = 0
-        for size in self.stage_sizes:
-            carrier = self.run_stage(carrier, cond, self.blocks[start:start + size])
-            start += size
+            carrier = self.run_literal(carrier, cond, context)
+        else:
+            start = 0
+            for size in self.stage_sizes:
+                carrier, context = self.run_stage(carrier, cond, self.blocks[start:start + size], start, context)
+                start += size
         b, hh, ww, c = carrier.shape
         return self.unpatchify(self.final_layer(carrier.reshape(b, hh * ww, c), cond))
+
+
+class SublayerSiHC(SiHC):
+    """Sublayer-wise SiHC (two connection events per block)."""
+
+    def __init__(self, **kw):
+        kw.setdefault("frequency", "sublayer")
+        super().__init__(**kw)
+
+
+class BlockwiseSiHC(SiHC):
+    """Block-wise SiHC (one connection event per block)."""
+
+    def __init__(self, **kw):
+        kw.setdefault("frequency", "block")
+        super().__init__(**kw)
 
 
 def sihc_b(**kw) -> SublayerSiHC:

@@ -151,6 +151,62 @@ def model_case(name, *, seed, depth, hidden, heads, patch):
     _save(name, meta, t=t, y=y.float(), x_sample=x.flatten()[::7], out_sample=out.detach().flatten()[::7], **state, **grads)
 
 
+def _open_gates(model, connections):
+    with torch.no_grad():   # non-zero gates, as research/tests/test_sublayer_kernels.py:229-242
+        for block in model.blocks:
+            block.branch.adaLN_modulation[-1].weight.normal_(std=0.01)
+            block.branch.adaLN_modulation[-1].bias.normal_(std=0.03)
+            for c in connections(block):
+                c.read_weight.add_(torch.randn_like(c.read_weight) * 0.01)
+                c.write_weight.add_(torch.randn_like(c.write_weight) * 0.02)
+        model.final_layer.linear.weight.normal_(std=0.03)
+        model.final_layer.adaLN_modulation[-1].weight.normal_(std=0.01)
+
+
+def _model_fixture(name, model, meta, grad_filter):
+    gen = torch.Generator().manual_seed(1234)
+    x = torch.randn(2, 3, 256, 256, generator=gen)
+    t = torch.rand(2, generator=gen)
+    y = torch.tensor([3, 977])
+    out = model(x, t, y)
+    out.float().square().mean().backward()
+    state = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    grads = {"grad::" + k: p.grad.detach().clone() for k, p in model.named_parameters() if grad_filter(k)}
+    meta = dict(meta, stride=29)
+    _save(name, meta, t=t, y=y.float(), x_sample=x.flatten()[::29], out_sample=out.detach().flatten()[::29], **state, **grads)
+
+
+def variant_model_cases():
+    """Block-wise model under the reference schedule, and the two in-context (class-prefix) models under the
+    reference's pure-torch factored control (``attach``, sihc/bench/fusion_controls.py:88-96), CPU fp32."""
+    from sihc.bench.fusion_controls import attach
+    from sihc.models.sihc.model import SiHCInContextModel
+    from sihc.models.sihc.reference import ReferenceSiHCModel
+    from sihc.models.sihc.sublayer import SublayerSiHCInContextModel
+    keep = lambda k: ("connection" in k or k.startswith("final_layer.linear") or "blocks.0.branch.attn.qkv" in k
+                      or k.startswith("x_embedder") or k == "in_context_posemb")
+    torch.manual_seed(23)
+    m = ReferenceSiHCModel(patch_size=8, hidden_size=32, depth=6, num_heads=4, workspace_grid=16,
+                           stage_sizes=(2, 4), attn_backend="math")
+    _open_gates(m, lambda b: [b.connection])
+    _model_fixture("model_block_tiny", m, dict(kind="block", depth=6, hidden=32, heads=4, patch=8, stages=[2, 4],
+                   ctx_len=0, ctx_start=0, source="sihc ReferenceSiHCModel (reference schedule), CPU fp32"), keep)
+    common = dict(patch_size=4, hidden_size=32, depth=8, num_heads=4, stage_sizes=(8,), in_context_len=8,
+                  in_context_start=2, attn_backend="math", repa_z_dims=(), repa_depth=None)
+    torch.manual_seed(29)
+    m = SublayerSiHCInContextModel(**common)
+    _open_gates(m, lambda b: [b.attention_connection, b.mlp_connection])
+    attach(m, "factored", "sublayer")
+    _model_fixture("model_ctx_sublayer_tiny", m, dict(kind="sublayer", depth=8, hidden=32, heads=4, patch=4, stages=[8],
+                   ctx_len=8, ctx_start=2, source="sihc SublayerSiHCInContextModel + factored torch control, CPU fp32"), keep)
+    torch.manual_seed(31)
+    m = SiHCInContextModel(kernel_backend="tuple", **common)
+    _open_gates(m, lambda b: [b.connection])
+    attach(m, "factored", "block")
+    _model_fixture("model_ctx_block_tiny", m, dict(kind="block", depth=8, hidden=32, heads=4, patch=4, stages=[8],
+                   ctx_len=8, ctx_start=2, source="sihc SiHCInContextModel + factored torch control, CPU fp32"), keep)
+
+
 def main(reference_root: str) -> None:
     sys.path[:0] = [reference_root, os.path.join(reference_root, "sihc")]
     from sihc.bench import fusion_controls as fc
@@ -176,6 +232,7 @@ def main(reference_root: str) -> None:
     stage_case("stage_p8", reference_module, seed=7, patch=8, c=5, events=3)
     stage_case("stage_p4", reference_module, seed=8, patch=4, c=3, events=4)
     model_case("model_tiny", seed=19, depth=8, hidden=32, heads=4, patch=8)
+    variant_model_cases()
 
 
 if __name__ == "__main__":

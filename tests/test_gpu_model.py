@@ -121,3 +121,26 @@ def test_literal_inference_schedule_matches_oracle_and_factored(dtype):
     with pytest.raises(RuntimeError):
         with torch.enable_grad():
             model.run_literal(torch.zeros(1, 32, 32, 32, device="cuda"), torch.zeros(1, 32, device="cuda"))
+
+
+@pytest.mark.parametrize("name", ["model_block_tiny", "model_ctx_sublayer_tiny", "model_ctx_block_tiny"])
+def test_blockwise_and_in_context_variants_on_gpu(name):
+    """Fused CUDA routing inside the block-wise and in-context models vs the reference models' own results."""
+    from test_model_cpu import build_variant
+    meta, t, model = build_variant(name)
+    x, tt, y = golden_inputs(meta, t)
+    model = model.cuda()
+    out = model(x.cuda(), tt.cuda(), y.cuda())
+    torch.testing.assert_close(out.flatten()[::meta["stride"]].cpu(), t["out_sample"], atol=3e-5, rtol=3e-4)
+    out.float().square().mean().backward()
+    checked = 0
+    for pname, p in model.named_parameters():
+        key = "grad::" + pname
+        if key in t:
+            torch.testing.assert_close(p.grad.cpu(), t[key], atol=3e-5, rtol=3e-3, msg=pname)
+            checked += 1
+    assert checked >= 15
+    with torch.no_grad():
+        model.inference_schedule = "literal"
+        lit = model(x.cuda(), tt.cuda(), y.cuda())
+    torch.testing.assert_close(lit, out.detach(), atol=3e-5, rtol=3e-4)

@@ -71,3 +71,37 @@ def test_literal_and_factored_oracle_schedules_agree():
         b = MO.factored_forward(model, x, tt, y)
     torch.testing.assert_close(a, b, atol=2e-5, rtol=2e-4)
     assert a.abs().mean() > 1e-3                       # gates are open: the output is not vacuous
+
+
+VARIANTS = ["model_block_tiny", "model_ctx_sublayer_tiny", "model_ctx_block_tiny"]
+
+
+def build_variant(name):
+    from residual_stream_burden_b200.model import SiHC
+    meta, t = load_golden(name)
+    model = SiHC(hidden_size=meta["hidden"], num_heads=meta["heads"], depth=meta["depth"],
+                 stage_sizes=tuple(meta["stages"]), patch_size=meta["patch"], frequency=meta["kind"],
+                 in_context_len=meta["ctx_len"], in_context_start=meta["ctx_start"])
+    model.load_state_dict({k: v for k, v in t.items() if k in model.state_dict()}, strict=True)
+    return meta, t, model
+
+
+@pytest.mark.parametrize("name", VARIANTS)
+def test_blockwise_and_in_context_variants_reproduce_reference_models(name):
+    """Block-wise events, and class-prefix context tokens in both frequencies: fixtures come from the
+    reference's ``ReferenceSiHCModel`` / ``SiHCInContextModel`` / ``SublayerSiHCInContextModel`` on CPU."""
+    from oracle import sihc_model_oracle as MO
+    meta, t, model = build_variant(name)
+    x, tt, y = golden_inputs(meta, t)
+    out = MO.factored_forward(model, x, tt, y)
+    torch.testing.assert_close(out.flatten()[::meta["stride"]], t["out_sample"], atol=2e-5, rtol=2e-4)
+    out.float().square().mean().backward()
+    checked = 0
+    for pname, p in model.named_parameters():
+        key = "grad::" + pname
+        if key in t:
+            torch.testing.assert_close(p.grad, t[key], atol=2e-6, rtol=2e-3, msg=pname)
+            checked += 1
+    assert checked >= 15
+    with torch.no_grad():
+        torch.testing.assert_close(MO.literal_forward(model, x, tt, y), out.detach(), atol=3e-5, rtol=3e-4)

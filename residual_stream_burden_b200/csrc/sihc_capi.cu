@@ -202,7 +202,7 @@ int sihc_read_fwd(const void* x, const void* alpha, void* const* out, int events
     Problem pb;
     if (int st = make_problem(pb, events, batch, grid, kh, kw, channels, dtype, wdtype, stream)) return st;
     if (!x || !alpha || !out) return SIHC_ERR_NULL;
-    VecChoice vc(vec_width(pb.dtype, pb.S), esize(dtype), pb.C);
+    VecChoice vc(events == 1 ? vec_width_fwd(pb.dtype, pb.S) : vec_width(pb.dtype, pb.S), esize(dtype), pb.C);
     vc.act(x); vc.weight(alpha, esize(wdtype));
     bool any = false;
     for (int l = 0; l < events; ++l) { vc.act(out[l]); any = any || out[l]; }
@@ -218,7 +218,7 @@ int sihc_write_fwd(const void* x, const void* const* dz, const void* beta, void*
     Problem pb;
     if (int st = make_problem(pb, events, batch, grid, kh, kw, channels, dtype, wdtype, stream)) return st;
     if (!dz || !beta || !y) return SIHC_ERR_NULL;
-    VecChoice vc(vec_width(pb.dtype, pb.S), esize(dtype), pb.C);
+    VecChoice vc(events == 1 && dz[0] ? vec_width_fwd(pb.dtype, pb.S) : vec_width(pb.dtype, pb.S), esize(dtype), pb.C);
     vc.act(x); vc.act(y); vc.weight(beta, esize(wdtype));
     for (int l = 0; l < events; ++l) vc.act(dz[l]);
     if (!vc.elem_ok) return SIHC_ERR_ALIGN;

@@ -20,6 +20,19 @@ inline int vec_width(DType dtype, int S) {
     return full < cap ? full : cap;
 }
 
+// Single-event forward kernels hold one coefficient set and no accumulators: they can afford twice the
+// per-thread footprint (S*V <= 64), i.e. full 16-byte vectors up to n = 8 and 8-byte vectors at n = 16.
+template <typename T, int S> struct VecWidthFwd {
+    static constexpr int kFull = 16 / int(sizeof(T));
+    static constexpr int kCap = 64 / S;
+    static constexpr int value = kFull < kCap ? kFull : kCap;
+};
+inline int vec_width_fwd(DType dtype, int S) {
+    const int full = dtype == kBF16 ? 8 : 4;
+    const int cap = S > 0 ? 64 / S : full;
+    return full < cap ? full : cap;
+}
+
 template <int N> using Int = std::integral_constant<int, N>;
 
 // f(T tag, W tag): (fp32,fp32), (bf16,bf16), (bf16,fp32)

@@ -53,6 +53,7 @@ cudaError_t launch_read_bwd1_ring(const Problem& pb, const void* x, const void* 
                                   float* partial, uint32_t* blocks, int stages, int threads);
 cudaError_t launch_write_bwd1_ring(const Problem& pb, const void* h, const void* dz, const void* beta, void* ddz,
                                    float* partial, uint32_t* blocks, int stages, int threads);
+struct WriteReadParams { const void* x; const void* dz; const void* beta; const void* alpha; void* y; void* z; Tiling t; };
 struct ReadBwd1Params { const void* x; const void* g; const void* w; void* dx; float* partial; Tiling t; };
 struct WriteBwd1Params { const void* h; const void* dz; const void* w; void* ddz; float* partial; Tiling t; };
 // Multi-event weight gradient partials: [P][E][S][C].

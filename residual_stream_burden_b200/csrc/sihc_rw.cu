@@ -194,8 +194,6 @@ __global__ void __launch_bounds__(kMaxThreads) write_fwd_kernel(const __grid_con
 // z[m,c]   = sum_s alpha_next[c,s] * y[m,s,c] (read from the ROUNDED carrier, as the unfused path reads it)
 // Moves 2S+2 elements per (token, channel); the unfused pair moves 3S+2.  `y` may be `x` (in place): every
 // element is read and written by the same thread.
-struct WriteReadParams { const void* x; const void* dz; const void* beta; const void* alpha; void* y; void* z; Tiling t; };
-
 template <typename T, typename W, int S, int V, int TT>
 __global__ void __launch_bounds__(kMaxThreads) write_read_kernel(const __grid_constant__ WriteReadParams p) {
     typedef VecIO<T, V> IO;
@@ -390,10 +388,13 @@ cudaError_t launch_read_fwd(const Problem& pb, const void* x, const void* alpha,
         using T = decltype(tt_); using W = decltype(ww_);
         return dispatch_slots(pb.S, [&](auto s_) {
             constexpr int S = decltype(s_)::value;
-            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(pb.E == 1 ? kReadFwdTT : 2), [&](auto v_, auto t_) {
-                constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
-                if (pb.E == 1)
+            if (pb.E == 1)      // pb.V was chosen with vec_width_fwd by the caller; n = 8 wants two tokens per thread
+                return dispatch_vec_tt<VecWidthFwd<T, S>::value>(pb.V, pick_tt(S == 8 ? 2 : kReadFwdTT), [&](auto v_, auto t_) {
+                    constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
                     return launch_persistent(read_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kReadFwdThreads, 1, false, nullptr);
+                });
+            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(2), [&](auto v_, auto t_) {
+                constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
                 return launch_persistent(read_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, 512, 1, false, nullptr);
             });
         });
@@ -408,10 +409,13 @@ cudaError_t launch_write_fwd(const Problem& pb, const void* x, const void* const
         using T = decltype(tt_); using W = decltype(ww_);
         return dispatch_slots(pb.S, [&](auto s_) {
             constexpr int S = decltype(s_)::value;
+            if (pb.E == 1 && dz[0] != nullptr)      // pb.V was chosen with vec_width_fwd by the caller
+                return dispatch_vec_tt<VecWidthFwd<T, S>::value>(pb.V, pick_tt(VecWidthFwd<T, S>::value * S >= 64 ? 1 : kWriteFwdTT), [&](auto v_, auto t_) {
+                    constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
+                    return launch_persistent(write_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kWriteFwdThreads, 1, false, nullptr);
+                });
             return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kWriteFwdTT), [&](auto v_, auto t_) {
                 constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
-                if (pb.E == 1 && dz[0] != nullptr)
-                    return launch_persistent(write_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kWriteFwdThreads, 1, false, nullptr);
                 return launch_persistent(write_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, 512, 1, false, nullptr);
             });
         });

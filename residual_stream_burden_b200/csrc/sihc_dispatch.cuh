@@ -66,10 +66,10 @@ inline cudaError_t dispatch_vec_tt(int V, int tt, F&& f) {
 // Fill the tiling and launch a persistent kernel; returns the x-grid used.
 template <typename K, typename P>
 inline cudaError_t launch_persistent(K kernel, P& params, const Problem& pb, int V, int TT, int default_threads,
-                                     uint32_t gz, bool emits_partials, uint32_t* gx_out) {
+                                     uint32_t gz, bool emits_partials, uint32_t* gx_out, int max_threads = kMaxThreads) {
     const Tuning& tn = tuning();
     const uint32_t ncv = pb.C / static_cast<uint32_t>(V);
-    const BlockShape bs = block_shape(ncv, tn.threads > 0 ? tn.threads : default_threads);
+    const BlockShape bs = block_shape(ncv, tn.threads > 0 ? tn.threads : default_threads, max_threads);
     Tiling& t = params.t;
     t.M = pb.M; t.g = pb.g; t.C = pb.C; t.ncv = ncv; t.cl = bs.cl; t.tl = bs.tl;
     const uint32_t per_tile = bs.tl * static_cast<uint32_t>(TT);

@@ -70,14 +70,15 @@ cudaError_t launch_tri_bwd(const Problem& pb, const void* grad, const void* cons
 // ---- shared launch plumbing -------------------------------------------------------------------
 struct BlockShape { uint32_t cl, tl, gy, threads; };
 
-inline BlockShape block_shape(uint32_t ncv, int target_threads) {
+inline BlockShape block_shape(uint32_t ncv, int target_threads, int max_threads = kMaxThreads) {
     BlockShape b;
     const uint32_t target = static_cast<uint32_t>(target_threads);
-    if (ncv <= static_cast<uint32_t>(kMaxThreads)) { b.cl = ncv; b.gy = 1; }
+    const uint32_t limit = static_cast<uint32_t>(max_threads);      // the kernel's __launch_bounds__
+    if (ncv <= limit) { b.cl = ncv; b.gy = 1; }
     else { b.cl = 256; b.gy = (ncv + 255) / 256; }
     uint32_t tl = (target + b.cl / 2) / b.cl;
     if (tl < 1) tl = 1;
-    while (tl > 1 && tl * b.cl > static_cast<uint32_t>(kMaxThreads)) --tl;
+    while (tl > 1 && tl * b.cl > limit) --tl;
     b.tl = tl;
     b.threads = b.cl * b.tl;
     return b;

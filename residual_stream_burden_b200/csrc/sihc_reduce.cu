@@ -284,7 +284,6 @@ __global__ void __launch_bounds__(kMaxThreads) tri_bwd_kernel(const __grid_const
 
 // ---- host launchers ------------------------------------------------------------------------------
 namespace {
-constexpr int kThreads = 384;
 constexpr int kTT = 2;
 inline int pick_tt(int dflt) { return tuning().tt > 0 ? tuning().tt : dflt; }
 
@@ -315,7 +314,7 @@ cudaError_t launch_wgrad(const Problem& pb, const void* carrier, const void* con
                 constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
                 constexpr int EC = EventChunk<S, V>::value;
                 const uint32_t gz = static_cast<uint32_t>((pb.E + EC - 1) / EC);
-                return launch_persistent(wgrad_kernel<T, S, V, TT>, p, pb, V, TT, kThreads, gz, true, blocks);
+                return launch_persistent(wgrad_kernel<T, S, V, TT>, p, pb, V, TT, 512, gz, true, blocks);
             });
         });
     });

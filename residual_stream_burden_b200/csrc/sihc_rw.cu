@@ -24,7 +24,7 @@ struct WriteFwdParams { const void* x; ConstPtrs dz; const void* w; void* y; int
 // (reference: `_read`, sihc/models/sihc/sublayer_kernels.py:28-49; E = 1: `read_torch`,
 //  sihc/bench/fusion_controls.py:14-20)
 template <typename T, typename W, int S, int V, int TT, bool SINGLE>
-__global__ void __launch_bounds__(kMaxThreads) read_fwd_kernel(const __grid_constant__ ReadFwdParams p) {
+__global__ void __launch_bounds__(SINGLE || TT < 4 ? kMaxThreads : 384) read_fwd_kernel(const __grid_constant__ ReadFwdParams p) {
     typedef VecIO<T, V> IO;
     typedef typename IO::Raw Raw;
     const Tiling& t = p.t;
@@ -393,9 +393,13 @@ cudaError_t launch_read_fwd(const Problem& pb, const void* x, const void* alpha,
                     constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
                     return launch_persistent(read_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kReadFwdThreads, 1, false, nullptr);
                 });
-            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(2), [&](auto v_, auto t_) {
+            // The stage read is limited by re-fetching each event's coefficients from L1: four tokens per thread
+            // halve that traffic (E=24, n=4: 3964 -> 4598 GB/s); the packed carrier vectors of four tokens fit the
+            // 168-register budget of a 384-thread block for S*V <= 32.
+            return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(4), [&](auto v_, auto t_) {
                 constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
-                return launch_persistent(read_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, 512, 1, false, nullptr);
+                return launch_persistent(read_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, TT >= 4 ? 384 : 512, 1, false, nullptr,
+                                         TT >= 4 ? 384 : kMaxThreads);
             });
         });
     });

@@ -118,6 +118,8 @@ CASES = [
     (16, 3, 11, 67, 16, torch.bfloat16, True),
     (16, 1, 16, 256, 8, torch.float32, False),
     (4, 9, 16, 768, 16, torch.bfloat16, False),
+    (4, 1, 4, 3200, 3, torch.bfloat16, False),       # 400 channel vectors: wider than a 384-thread block
+    (4, 2, 16, 1152, 24, torch.bfloat16, True),
 ]
 
 

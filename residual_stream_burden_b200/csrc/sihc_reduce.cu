@@ -194,10 +194,11 @@ __global__ void __launch_bounds__(kMaxThreads) tri_fwd_kernel(const __grid_const
 // ddz_l = grad * gamma_l (optional); partial[block][l][c] = sum_{m in block} grad[m,c] * dz_l[m,c]
 // for the JC events of blockIdx.z  (reference: `_tri_autograd`, `_triangular_gamma_grad`,
 // sihc/models/sihc/sublayer_kernels.py:369-379, :324-334).
+// JC = event slots per z-slice (2, 4 or 8), TT = tokens per thread; JC*TT update vectors are in flight per
+// thread, so short prefixes trade unused event slots for more tokens.
 constexpr int kTriChunk = 8;
-template <typename T, typename W, int V, int TT>
+template <typename T, typename W, int V, int TT, int JC>
 __global__ void __launch_bounds__(kMaxThreads) tri_bwd_kernel(const __grid_constant__ TriBwdParams p) {
-    constexpr int JC = kTriChunk;
     __shared__ float red[kMaxThreads * V];
     const Tiling& t = p.t;
     const Lane ln = make_lane<V>(t);
@@ -348,17 +349,20 @@ cudaError_t launch_tri_bwd(const Problem& pb, const void* grad, const void* cons
     TriBwdParams p{};
     p.grad = grad; p.gamma = gamma; p.partial = partial; p.J = pb.E; p.has_ddz = ddz != nullptr;
     for (int l = 0; l < pb.E; ++l) { p.dz.p[l] = dz[l]; p.ddz.p[l] = ddz ? ddz[l] : nullptr; }
+    const uint32_t gz = static_cast<uint32_t>((pb.E + kTriChunk - 1) / kTriChunk);
+    p.chunk = (pb.E + static_cast<int>(gz) - 1) / static_cast<int>(gz);     // e.g. 12 events -> 2 slices of 6
+    const int forced_tt = tuning().tt;
     return dispatch_types(pb.dtype, pb.wdtype, [&](auto tt_, auto ww_) {
         using T = decltype(tt_); using W = decltype(ww_);
-        return dispatch_tri_vec(pb.dtype, pb.V, pick_tt(1), [&](auto v_, auto t_) {
-            constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
-            if constexpr (V > 16 / int(sizeof(T))) return cudaErrorInvalidValue;
-            else {
-                const uint32_t gz = static_cast<uint32_t>((pb.E + kTriChunk - 1) / kTriChunk);
-                p.chunk = (pb.E + static_cast<int>(gz) - 1) / static_cast<int>(gz);     // e.g. 12 events -> 2 slices of 6
-                return launch_persistent(tri_bwd_kernel<T, W, V, TT>, p, pb, V, TT, 512, gz, partial != nullptr, blocks);
-            }
-        });
+        constexpr int VF = 16 / int(sizeof(T));
+        auto go = [&](auto v_, auto t_, auto j_) {
+            constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value; constexpr int JC = decltype(j_)::value;
+            return launch_persistent(tri_bwd_kernel<T, W, V, TT, JC>, p, pb, V, TT, 512, gz, partial != nullptr, blocks);
+        };
+        if (pb.V == 1) return go(Int<1>{}, Int<1>{}, Int<8>{});
+        if (forced_tt <= 0 && p.chunk <= 2) return go(Int<VF>{}, Int<4>{}, Int<2>{});
+        if (forced_tt <= 0 && p.chunk <= 4) return go(Int<VF>{}, Int<2>{}, Int<4>{});
+        return go(Int<VF>{}, Int<1>{}, Int<8>{});
     });
 }
 

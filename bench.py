@@ -461,6 +461,7 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
     torch.manual_seed(1234 + rank)
     gen = torch.Generator().manual_seed(rank)
     launches0 = _lib.launch_count()
+    torch.cuda.reset_peak_memory_stats(device)
     if kind == "sihc_b_fwd":
         batch = 256
         model = sihc_b().to(device).eval()

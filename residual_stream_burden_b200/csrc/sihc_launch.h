@@ -20,6 +20,9 @@ struct Tuning {
     int maxvec_bytes = 0;   // cap on the vector width in bytes (0: 16)
     int ring = -1;          // stages of the async-copy ring in the fused single-event adjoints (-1: default, 0: off)
     int min_block_tokens = 0;   // fewest tokens a partial-sum block should own (0: default)
+    int stage_smem = -1;        // stage read/write coefficients: 1 staged in shared memory, 0 re-read from L1,
+                                // -1 default (shared memory for 8 or more slots, where it measured 15-25 % faster;
+                                // for 4 slots it measured 5-10 % slower)
 };
 Tuning& tuning();
 int sm_count();
@@ -53,6 +56,11 @@ cudaError_t launch_read_bwd1_ring(const Problem& pb, const void* x, const void* 
                                   float* partial, uint32_t* blocks, int stages, int threads);
 cudaError_t launch_write_bwd1_ring(const Problem& pb, const void* h, const void* dz, const void* beta, void* ddz,
                                    float* partial, uint32_t* blocks, int stages, int threads);
+struct ReadFwdParams { const void* x; const void* w; MutPtrs out; int E; Tiling t; };
+struct WriteFwdParams { const void* x; ConstPtrs dz; const void* w; void* y; int E; Tiling t; };
+// Stage (multi-event) read / write with the block's coefficient slice staged once in shared memory.
+cudaError_t launch_read_fwd_stage(const Problem& pb, ReadFwdParams& p);
+cudaError_t launch_write_fwd_stage(const Problem& pb, WriteFwdParams& p);
 struct WriteReadParams { const void* x; const void* dz; const void* beta; const void* alpha; void* y; void* z; Tiling t; };
 struct ReadBwd1Params { const void* x; const void* g; const void* w; void* dx; float* partial; Tiling t; };
 struct WriteBwd1Params { const void* h; const void* dz; const void* w; void* ddz; float* partial; Tiling t; };

@@ -393,3 +393,27 @@ def test_channel_counts_wider_than_one_block(R, slots, c, events):
     y2, z2 = R.sihc_write_read(x.to(DEV), dz[0].to(DEV), beta[0].to(DEV), alpha[0].to(DEV))
     close(y2, O.write(x, [dz[0]], [beta[0]]), dtype, "write_read y")
     close(z2, O.read(O.write(x, [dz[0]], [beta[0]]), alpha[0]), dtype, "write_read z")
+
+
+@pytest.mark.parametrize("staged", [0, 1])
+@pytest.mark.parametrize("slots,events,c,dtype,wf32", [(4, 24, 768, torch.bfloat16, False), (16, 12, 256, torch.bfloat16, True),
+                                                       (8, 5, 1152, torch.bfloat16, False), (2, 3, 64, torch.float32, False)])
+def test_stage_read_write_coefficient_staging_variants(R, staged, slots, events, c, dtype, wf32):
+    """The stage read and write exist with their coefficients re-read from L1 or staged (transposed) in
+    shared memory, including channel counts split over several blocks; both against the oracle."""
+    from residual_stream_burden_b200 import _lib
+    torch.manual_seed(900 + slots + events)
+    kh, kw = O.cell_shape(slots)
+    wdtype = torch.float32 if wf32 else dtype
+    b, g = 2, 7
+    x = torch.randn(b, g * kh, g * kw, c).to(dtype)
+    alpha = (1.0 / slots + 0.05 * torch.randn(events, c, slots)).to(wdtype)
+    dz = [torch.randn(b, g * g, c).to(dtype) for _ in range(events)]
+    _lib.tune("stage_smem", staged)
+    try:
+        z = R.sublayer_read(x.to(DEV), alpha.to(DEV))
+        y = R.sublayer_write(x.to(DEV), [t.to(DEV) for t in dz], alpha.to(DEV))
+    finally:
+        _lib.tune("stage_smem_default", 0)
+    close(torch.stack(z), torch.stack(O.multi_read(x, alpha)), dtype, "z")
+    close(y, O.write(x, dz, alpha), dtype, "y")

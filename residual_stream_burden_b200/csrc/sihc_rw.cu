@@ -391,7 +391,7 @@ cudaError_t launch_read_fwd(const Problem& pb, const void* x, const void* alpha,
                     constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
                     return launch_persistent(read_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kReadFwdThreads, 1, false, nullptr);
                 });
-            if ((tuning().stage_smem < 0 ? S >= 8 : tuning().stage_smem != 0) && pb.V > 1) return launch_read_fwd_stage(pb, p);
+            if ((tuning().stage_smem != 0) && pb.V > 1) return launch_read_fwd_stage(pb, p);
             // The stage read is limited by re-fetching each event's coefficients from L1: four tokens per thread
             // halve that traffic (E=24, n=4: 3964 -> 4598 GB/s); the packed carrier vectors of four tokens fit the
             // 168-register budget of a 384-thread block for S*V <= 32.
@@ -417,7 +417,7 @@ cudaError_t launch_write_fwd(const Problem& pb, const void* x, const void* const
                     constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
                     return launch_persistent(write_fwd_kernel<T, W, S, V, TT, true>, p, pb, V, TT, kWriteFwdThreads, 1, false, nullptr);
                 });
-            if ((tuning().stage_smem < 0 ? S >= 8 : tuning().stage_smem != 0) && pb.V > 1) return launch_write_fwd_stage(pb, p);
+            if ((tuning().stage_smem != 0) && pb.V > 1) return launch_write_fwd_stage(pb, p);
             return dispatch_vec_tt<VecWidth<T, S>::value>(pb.V, pick_tt(kWriteFwdTT), [&](auto v_, auto t_) {
                 constexpr int V = decltype(v_)::value; constexpr int TT = decltype(t_)::value;
                 return launch_persistent(write_fwd_kernel<T, W, S, V, TT, false>, p, pb, V, TT, 512, 1, false, nullptr);

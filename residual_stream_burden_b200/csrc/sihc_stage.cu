@@ -8,9 +8,10 @@
 // global memory (`alpha.transpose(1, 2).contiguous()`, sihc/models/sihc/sublayer_kernels.py:224); this
 // library allocates nothing, so the transpose lives in shared memory.
 //
-// Measured on B200 (bf16, width 768): 16 slots E=12 read 2347 -> 2686 GB/s, write 2134 -> 2379; E=24 read
-// 1854 -> 2329, write 1517 -> 1799.  With 4 slots it is slower than re-reading from L1 (read 4599 -> 4118,
-// write 3945 -> 3761), so these kernels are the default only for 8 or more slots.
+// The slice is kept to ~50 KB (a narrower channel tile, more blocks per SM): these kernels are latency-bound, and
+// residency matters more than a wide tile.  Measured on B200 (bf16, width 768, against re-reading from L1):
+// 4 slots E=24 read 4599 -> 5074 GB/s, write 3945 -> 4517; 16 slots E=12 read 2347 -> 2938, write 2134 -> 2649.
+// With a 160 KB slice (one block per SM) the 4-slot case was slower than the L1 form (4118 / 3761).
 #include "sihc_dispatch.cuh"
 
 namespace sihc {
@@ -176,7 +177,7 @@ namespace {
 // dimension split evenly over blockIdx.y.
 struct StageShape { uint32_t cl, tl, gy, threads; size_t smem; };
 inline StageShape stage_shape(uint32_t ncv, int E, int S, int V, size_t wbytes, int target_threads) {
-    constexpr size_t kBudget = 160 * 1024;
+    const size_t kBudget = static_cast<size_t>(tuning().stage_budget_kb > 0 ? tuning().stage_budget_kb : 50) * 1024;
     const size_t per_lane = static_cast<size_t>(E) * S * V * wbytes;
     uint32_t max_cl = static_cast<uint32_t>(kBudget / per_lane);
     if (max_cl < 8) max_cl = 8;
@@ -218,10 +219,11 @@ cudaError_t launch_read_fwd_stage(const Problem& pb, ReadFwdParams& p) {
         return dispatch_slots(pb.S, [&](auto s_) {
             constexpr int S = decltype(s_)::value;
             constexpr int V = VecWidth<T, S>::value;
-            constexpr int TT = 4;
             const int threads = tuning().threads > 0 ? tuning().threads : 384;
             const StageShape sh = stage_shape(pb.C / V, pb.E, S, V, sizeof(W), threads);
-            return launch_stage(read_fwd_stage_kernel<T, W, S, V, TT>, p, pb, V, TT, sh);
+            if (tuning().tt > 0 && tuning().tt < 4)
+                return launch_stage(read_fwd_stage_kernel<T, W, S, V, 2>, p, pb, V, 2, sh);
+            return launch_stage(read_fwd_stage_kernel<T, W, S, V, 4>, p, pb, V, 4, sh);
         });
     });
 }
@@ -232,10 +234,11 @@ cudaError_t launch_write_fwd_stage(const Problem& pb, WriteFwdParams& p) {
         return dispatch_slots(pb.S, [&](auto s_) {
             constexpr int S = decltype(s_)::value;
             constexpr int V = VecWidth<T, S>::value;
-            constexpr int TT = 2;
             const int threads = tuning().threads > 0 ? tuning().threads : 384;
             const StageShape sh = stage_shape(pb.C / V, pb.E, S, V, sizeof(W), threads);
-            return launch_stage(write_fwd_stage_kernel<T, W, S, V, TT>, p, pb, V, TT, sh);
+            if (tuning().tt >= 2)
+                return launch_stage(write_fwd_stage_kernel<T, W, S, V, 2>, p, pb, V, 2, sh);
+            return launch_stage(write_fwd_stage_kernel<T, W, S, V, 1>, p, pb, V, 1, sh);
         });
     });
 }

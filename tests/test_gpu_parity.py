@@ -417,3 +417,44 @@ def test_stage_read_write_coefficient_staging_variants(R, staged, slots, events,
         _lib.tune("stage_smem_default", 0)
     close(torch.stack(z), torch.stack(O.multi_read(x, alpha)), dtype, "z")
     close(y, O.write(x, dz, alpha), dtype, "y")
+
+
+def _misaligned(t, dev=DEV):
+    """Same values, packed, but starting one element past a 16-byte boundary."""
+    flat = torch.empty(t.numel() + 1, dtype=t.dtype, device=dev)
+    view = flat[1:].view(t.shape)
+    view.copy_(t)
+    assert view.is_contiguous() and view.data_ptr() % 16 != 0
+    return view
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("events", [1, 3])
+def test_pointers_off_the_16_byte_grid_take_the_scalar_path(R, dtype, events):
+    """Packed tensors whose storage does not start on a 16-byte boundary are legal inputs; the library
+    must fall back to element-wise accesses rather than fault or mis-read."""
+    torch.manual_seed(314)
+    slots, b, g, c = 4, 2, 5, 64
+    x = torch.randn(b, 2 * g, 2 * g, c).to(dtype)
+    alpha = (0.25 + 0.05 * torch.randn(events, c, slots)).to(dtype)
+    dz = [torch.randn(b, g * g, c).to(dtype) for _ in range(events)]
+    gz = [torch.randn(b, g * g, c).to(dtype) for _ in range(events)]
+    gy = torch.randn(b, 2 * g, 2 * g, c).to(dtype)
+    xd, ad = _misaligned(x).requires_grad_(), _misaligned(alpha).requires_grad_()
+    dzd = [_misaligned(t).requires_grad_() for t in dz]
+    z = R.sublayer_read(xd, ad)
+    dx, dalpha = torch.autograd.grad(z, (xd, ad), [_misaligned(t) for t in gz])
+    y = R.sublayer_write(xd, dzd, ad)
+    _, dbeta, *ddz = torch.autograd.grad(y, (xd, ad, *dzd), _misaligned(gy))
+    close(torch.stack(z), torch.stack(O.multi_read(x, alpha)), dtype, "z")
+    close(y, O.write(x, dz, alpha), dtype, "y")
+    odx, oda = O.read_backward(x, gz, alpha, acc=torch.float64)
+    oddz, odb = O.write_backward(gy, dz, alpha, acc=torch.float64)
+    close(dx, odx, dtype, "dx")
+    close(dalpha, oda.to(dtype), dtype, "dalpha")
+    close(torch.stack(ddz), torch.stack(oddz), dtype, "ddz")
+    close(dbeta, odb.to(dtype), dtype, "dbeta")
+    base = _misaligned(torch.randn(b, g * g, c).to(dtype))
+    gamma = _misaligned((torch.randn(events, c) * 0.05).to(dtype))
+    out = R.sublayer_triangular(base, dzd, gamma)
+    close(out, O.triangular(base.cpu(), dz, gamma.cpu()), dtype, "triangular")

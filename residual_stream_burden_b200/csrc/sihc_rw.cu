@@ -1,11 +1,14 @@
 // SiHC read / write streaming kernels (forward, and the fused single-event adjoints).
 //
-// All four kernels are HBM-bound diagonal maps: per workspace token and channel
-// they touch S carrier elements and a handful of workspace elements, with at
-// most 2*S FMAs.  The design goal is therefore bytes in flight, not math:
-// every thread issues TT*(S+1) independent 16-byte loads before its first use,
-// coefficient vectors live in registers (single event) or come from L1 in the
-// native [E,C,S] layout (stage ops), and results leave as 16-byte streaming stores.
+// The single-event kernels are HBM-bound diagonal maps: per workspace token and
+// channel they touch S carrier elements and a handful of workspace elements, with
+// at most 2*S FMAs.  The design goal is therefore bytes in flight, not math: every
+// thread issues TT*(S+1) independent 16-byte loads (read-only path) before its
+// first use, keeps its coefficient vectors in registers, and stores 16-byte
+// streaming vectors.  The multi-event forms in this file fetch each event's
+// coefficients from L1 in the native [E,C,S] layout; they serve the scalar path -
+// on the vector path the stage read and write run the staged-coefficient kernels
+// of sihc_stage.cu, and the fused adjoints the ring kernels of sihc_ring.cu.
 //
 // Algorithmic traffic per (token, channel) element, in elements:
 //   read  fwd : S + E          write fwd : 2S + E (S + E without the carry)
@@ -14,8 +17,6 @@
 #include "sihc_dispatch.cuh"
 
 namespace sihc {
-
-
 
 // ---- stage read, forward ---------------------------------------------------------------------
 // out[l][m,c] = sum_s alpha[l,c,s] * X[m,s,c]

@@ -69,7 +69,7 @@ void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::m
 uint32_t partial_blocks_bound(uint32_t M) {
     const int cap = tuning().rbps > 0 ? tuning().rbps : 2;
     uint32_t by_sm = static_cast<uint32_t>(sm_count()) * static_cast<uint32_t>(cap);
-    const uint32_t per = tuning().min_block_tokens > 0 ? static_cast<uint32_t>(tuning().min_block_tokens) : 64u;
+    const uint32_t per = tuning().min_block_tokens > 0 ? static_cast<uint32_t>(tuning().min_block_tokens) : 32u;
     uint32_t by_tokens = (M + per - 1) / per;      // a block should own at least this many tokens
     if (by_tokens < 1) by_tokens = 1;
     return by_sm < by_tokens ? by_sm : by_tokens;

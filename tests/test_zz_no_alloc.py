@@ -50,7 +50,7 @@ def test_static_scratch_matches_workspace_entry_point_twice(dtype, events, slots
     lib = _lib.lib
     code = _lib.BF16 if dtype == torch.bfloat16 else _lib.F32
     kh, kw = CELLS[slots]
-    b, g, c = 24, 16, 768                      # 6144 tokens -> 96 partial-sum blocks
+    b, g, c = 24, 16, 768                      # 6144 tokens -> 192 partial-sum blocks
     torch.manual_seed(2024)
     for call in range(2):                      # the second call reuses the array the first one filled
         x = torch.randn(b, g * kh, g * kw, c, device=DEV).to(dtype) * (1.0 + call)

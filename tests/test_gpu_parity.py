@@ -285,6 +285,63 @@ def test_large_size_properties(R):
     assert torch.equal(y0.view(b * g, 2, g, 2, c), gz.view(b * g, 1, g, 1, c).expand(b * g, 2, g, 2, c))
 
 
+def test_full_size_integer_inputs_are_bit_exact(R):
+    """The bench workload's full size (2^20 tokens, 4 slots, width 768, bf16 carrier, fp32 weights) with
+    small-integer inputs.  Every product and every partial sum is then an integer below 2^24 (weight
+    gradients: |x*g| <= 4 over 2^20 tokens) resp. 2^8 (bf16 outputs), so fp32 accumulation is exact in any
+    order and every kernel must reproduce integer arithmetic bit for bit: forward values, both adjoint maps,
+    the token-reduced weight gradients, the fused write+read step and the triangular pair."""
+    torch.manual_seed(5)
+    b, g, c, s = 4096, 16, 768, 4
+    dtype = torch.bfloat16
+
+    def ints(*shape, dt=dtype):
+        return torch.randint(-2, 3, shape, device=DEV, dtype=torch.int8).to(dt)
+
+    x = ints(b, 2 * g, 2 * g, c)                                 # 6.4 GB
+    gz = ints(b, g * g, c)
+    alpha, beta = ints(1, c, s, dt=torch.float32), ints(1, c, s, dt=torch.float32)
+    rows, step = b * g, 4096
+    slot_map = lambda w: w[0].T.reshape(1, 2, 1, 2, c)           # [C,S] -> broadcast over [rows, uy, wx, ux, C]
+    cells = lambda t: t.view(rows, 2, g, 2, c)
+    tokens = lambda t: t.view(rows, 1, g, 1, c)
+
+    z = R.sublayer_read(x, alpha)[0]
+    dx, dalpha = R.ops._read_backward_op(x, [gz], alpha, True, True)
+    y = R.sublayer_write(x, [gz], beta)
+    ddz, dbeta = R.ops._write_backward_op(x, [gz], beta, True, True)
+    y2, z2 = R.sihc_write_read(x, gz, beta[0].contiguous(), alpha[0].contiguous())
+    assert dalpha.dtype == torch.float32 and dbeta.dtype == torch.float32
+    wsum = torch.zeros(2, 2, c, dtype=torch.float64, device=DEV)
+    for lo in range(0, rows, step):
+        sl = slice(lo, lo + step)
+        xc, gt = cells(x)[sl].float(), tokens(gz)[sl].float()
+        assert torch.equal(z.view(rows, g, c)[sl], (xc * slot_map(alpha)).sum((1, 3)).to(dtype)), lo
+        assert torch.equal(cells(dx)[sl], (gt * slot_map(alpha)).to(dtype).expand_as(xc)), lo
+        yc = xc + gt * slot_map(beta)
+        assert torch.equal(cells(y)[sl], yc.to(dtype)), lo
+        assert torch.equal(ddz[0].view(rows, g, c)[sl], (xc * slot_map(beta)).sum((1, 3)).to(dtype)), lo
+        assert torch.equal(cells(y2)[sl], yc.to(dtype)), lo
+        assert torch.equal(z2.view(rows, g, c)[sl], (yc * slot_map(alpha)).sum((1, 3)).to(dtype)), lo
+        wsum += (xc * gt).double().sum((0, 2))
+    expected = wsum.reshape(s, c).T.float()                       # sum_m x[m,s,c] * g[m,c]
+    assert float(expected.abs().max()) < 2 ** 24
+    assert torch.equal(dalpha[0], expected)
+    assert torch.equal(dbeta[0], expected)                        # same sum: carrier gradient = x, update = gz
+    del dx, y, y2, z2, ddz
+
+    ups = [ints(b, g * g, c) for _ in range(3)]
+    gamma = ints(3, c, dt=torch.float32)
+    out = R.sublayer_triangular(z, ups, gamma)
+    dd, dgamma = R.ops._tri_backward_op(gz, ups, gamma, True, True)
+    acc = z.float()
+    for l, u in enumerate(ups):
+        acc += u.float() * gamma[l]
+        assert torch.equal(dd[l], (gz.float() * gamma[l]).to(dtype)), l
+        assert torch.equal(dgamma[l], (gz.double() * u.double()).sum((0, 1)).float()), l
+    assert torch.equal(out, acc.to(dtype))
+
+
 def test_c_abi_direct_calls_and_status_codes(R):
     """Raw ctypes calls: status codes for bad arguments, no torch op layer in between."""
     from residual_stream_burden_b200 import _lib

@@ -397,6 +397,29 @@ def test_single_event_adjoints_register_and_ring_variants(R, stages, slots, dtyp
     close(got["dbeta"], odb.to(dtype), dtype, "dbeta")
 
 
+@pytest.mark.parametrize("active,c,dtype,gamma_fp32", [(3, 64, torch.bfloat16, False), (5, 768, torch.bfloat16, True),
+                                                       (8, 128, torch.float32, True), (12, 1152, torch.bfloat16, False),
+                                                       (23, 768, torch.bfloat16, False), (23, 64, torch.bfloat16, True)])
+def test_triangular_backward_event_slices_and_single_outputs(R, active, c, dtype, gamma_fp32):
+    """The triangular backward must match the oracle for every chunking of the events (1, 2 or 3 slices of at
+    most 8), both gamma dtypes and a token count that is not a multiple of any tile; asking for only one of
+    the two outputs must give the same bits as asking for both."""
+    torch.manual_seed(291 + active)
+    b, n = 3, 83                                          # 249 tokens
+    ups = [torch.randn(b, n, c).to(dtype) for _ in range(active)]
+    gamma = (torch.randn(active, c) * 0.05).to(torch.float32 if gamma_fp32 else dtype)
+    grad = torch.randn(b, n, c).to(dtype)
+    ud, gd, gr = [u.to(DEV) for u in ups], gamma.to(DEV), grad.to(DEV)
+    ddz, dgamma = R.ops._tri_backward_op(gr, ud, gd, True, True)
+    ddz_only, _ = R.ops._tri_backward_op(gr, ud, gd, True, False)
+    _, dgamma_only = R.ops._tri_backward_op(gr, ud, gd, False, True)
+    oddz, odg = O.triangular_backward(grad, ups, gamma, acc=torch.float64)
+    close(torch.stack(ddz), torch.stack(oddz), dtype, "ddz")
+    close(dgamma, odg.to(gamma.dtype), gamma.dtype, "dgamma")
+    assert all(torch.equal(a, b_) for a, b_ in zip(ddz, ddz_only))
+    assert torch.equal(dgamma, dgamma_only)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("slots,b,g,c", [(4, 3, 7, 67), (4, 4, 16, 768), (2, 2, 5, 64), (8, 2, 6, 128), (16, 2, 4, 64)])
 def test_fused_write_then_read_step_is_the_unfused_pair(R, slots, b, g, c, dtype):

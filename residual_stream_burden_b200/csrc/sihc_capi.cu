@@ -192,6 +192,7 @@ int sihc_tune(const char* name, int value) {
     else if (!std::strcmp(name, "ring_default")) t.ring = -1;            // back to the per-kernel default
     else if (!std::strcmp(name, "min_block_tokens")) t.min_block_tokens = value;
     else if (!std::strcmp(name, "stage_budget_kb")) t.stage_budget_kb = value;
+    else if (!std::strcmp(name, "tri_chunk")) t.tri_chunk = value;
     else if (!std::strcmp(name, "stage_smem")) t.stage_smem = value;
     else if (!std::strcmp(name, "stage_smem_default")) t.stage_smem = -1;
     else return SIHC_ERR_NULL;

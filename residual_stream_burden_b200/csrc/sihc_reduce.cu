@@ -196,14 +196,19 @@ __global__ void __launch_bounds__(kMaxThreads) tri_fwd_kernel(const __grid_const
 // sihc/models/sihc/sublayer_kernels.py:369-379, :324-334).
 // JC = event slots per z-slice (2, 4 or 8), TT = tokens per thread; JC*TT update vectors are in flight per
 // thread, so short prefixes trade unused event slots for more tokens.
-constexpr int kTriChunk = 8;
+// Events per z-slice (the largest the kernel is built for, and the default).  Measured on B200, bf16, both outputs:
+// slices of at most 4 events with two tokens per thread beat slices of up to 8 with one token for every J >= 5
+// (width 768, 65 536 tokens: J=12 5271 -> 6085, J=23 5559 -> 6034 GB/s; width 1152, 8192 tokens: J=23 4743 -> 5271).
+constexpr int kTriMaxChunk = 8;
+constexpr int kTriChunk = 4;
 template <typename T, typename W, int V, int TT, int JC>
 __global__ void __launch_bounds__(kMaxThreads) tri_bwd_kernel(const __grid_constant__ TriBwdParams p) {
     __shared__ float red[kMaxThreads * V];
     const Tiling& t = p.t;
     const Lane ln = make_lane<V>(t);
-    const int e0 = blockIdx.z * p.chunk;          // p.chunk <= JC events per z-slice, balanced across slices
-    const int e1 = e0 + p.chunk < p.J ? e0 + p.chunk : p.J;
+    // events [e0, e1) of this z-slice: J spread over the slices so that they differ by at most one (<= JC each)
+    const int e0 = static_cast<int>(blockIdx.z) * p.J / static_cast<int>(gridDim.z);
+    const int e1 = static_cast<int>(blockIdx.z + 1) * p.J / static_cast<int>(gridDim.z);
     const T* __restrict__ grad = static_cast<const T*>(p.grad) + ln.c0;
     float acc[JC][V];
 #pragma unroll
@@ -349,8 +354,9 @@ cudaError_t launch_tri_bwd(const Problem& pb, const void* grad, const void* cons
     TriBwdParams p{};
     p.grad = grad; p.gamma = gamma; p.partial = partial; p.J = pb.E; p.has_ddz = ddz != nullptr;
     for (int l = 0; l < pb.E; ++l) { p.dz.p[l] = dz[l]; p.ddz.p[l] = ddz ? ddz[l] : nullptr; }
-    const uint32_t gz = static_cast<uint32_t>((pb.E + kTriChunk - 1) / kTriChunk);
-    p.chunk = (pb.E + static_cast<int>(gz) - 1) / static_cast<int>(gz);     // e.g. 12 events -> 2 slices of 6
+    const int max_chunk = tuning().tri_chunk > 0 && tuning().tri_chunk <= kTriMaxChunk ? tuning().tri_chunk : kTriChunk;
+    const uint32_t gz = static_cast<uint32_t>((pb.E + max_chunk - 1) / max_chunk);
+    p.chunk = (pb.E + static_cast<int>(gz) - 1) / static_cast<int>(gz);     // largest slice, e.g. 13 events -> 4, 3, 3, 3
     const int forced_tt = tuning().tt;
     return dispatch_types(pb.dtype, pb.wdtype, [&](auto tt_, auto ww_) {
         using T = decltype(tt_); using W = decltype(ww_);

@@ -100,6 +100,27 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
+// acc += a * b for the two bf16 pairs packed in a and b, each product formed exactly and added to the fp32
+// accumulator with one rounding (`fma.rn.f32.bf16`, sm_100+): the same value as fmaf(float(a), float(b), acc)
+// without spending integer-pipe instructions on widening the operands first.
+#ifndef SIHC_MIXED_FMA
+#define SIHC_MIXED_FMA 1
+#endif
+__device__ __forceinline__ void fma_bf16x2(uint32_t a, uint32_t b, float& acc_lo, float& acc_hi) {
+#if SIHC_MIXED_FMA
+    asm("{\n\t"
+        ".reg .b16 al, ah, bl, bh;\n\t"
+        "mov.b32 {al, ah}, %2;\n\t"
+        "mov.b32 {bl, bh}, %3;\n\t"
+        "fma.rn.f32.bf16 %0, al, bl, %0;\n\t"
+        "fma.rn.f32.bf16 %1, ah, bh, %1;\n\t"
+        "}"
+        : "+f"(acc_lo), "+f"(acc_hi) : "r"(a), "r"(b));
+#else
+    acc_lo = fmaf(__uint_as_float(a << 16), __uint_as_float(b << 16), acc_lo);
+    acc_hi = fmaf(__uint_as_float(a & 0xffff0000u), __uint_as_float(b & 0xffff0000u), acc_hi);
+#endif
+}
 __device__ __forceinline__ bf16_t pack_bf16(float f) {
     bf16_t r;
     asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(f));
@@ -127,11 +148,23 @@ template <int V> struct VecIO<float, V> {
         else if constexpr (V == 2) { f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); }
         else { f[0] = __uint_as_float(r); }
     }
+    static __device__ __forceinline__ void fma_raw(const Raw& a, const Raw& b, float (&acc)[V]) {   // acc += a * b
+        float fa[V], fb[V];
+        unpack(a, fa); unpack(b, fb);
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = fmaf(fa[v], fb[v], acc[v]);
+    }
     static __device__ __forceinline__ void load(const float* p, float (&f)[V]) {
         if constexpr (V == 4) { float4 q = ld_stream(reinterpret_cast<const float4*>(p)); f[0] = q.x; f[1] = q.y; f[2] = q.z; f[3] = q.w; }
         else if constexpr (V == 2) { float2 q = ld_stream(reinterpret_cast<const float2*>(p)); f[0] = q.x; f[1] = q.y; }
         else { f[0] = ld_stream(p); }
     }
+    static __device__ __forceinline__ Raw pack(const float (&f)[V]) {
+        if constexpr (V == 4) return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+        else if constexpr (V == 2) return make_uint2(__float_as_uint(f[0]), __float_as_uint(f[1]));
+        else return __float_as_uint(f[0]);
+    }
+    static __device__ __forceinline__ void store_raw(float* p, const Raw& r) { st_stream(reinterpret_cast<Raw*>(p), r); }
     static __device__ __forceinline__ void store(float* p, const float (&f)[V]) {
         if constexpr (V == 4) st_stream(reinterpret_cast<float4*>(p), make_float4(f[0], f[1], f[2], f[3]));
         else if constexpr (V == 2) st_stream(reinterpret_cast<float2*>(p), make_float2(f[0], f[1]));
@@ -156,6 +189,18 @@ template <int V> struct VecIO<bf16_t, V> {
             f[0] = __uint_as_float(static_cast<uint32_t>(r) << 16);
         }
     }
+    static __device__ __forceinline__ void fma_raw(const Raw& a, const Raw& b, float (&acc)[V]) {   // acc += a * b
+        if constexpr (V == 8) {
+            fma_bf16x2(a.x, b.x, acc[0], acc[1]); fma_bf16x2(a.y, b.y, acc[2], acc[3]);
+            fma_bf16x2(a.z, b.z, acc[4], acc[5]); fma_bf16x2(a.w, b.w, acc[6], acc[7]);
+        } else if constexpr (V == 4) {
+            fma_bf16x2(a.x, b.x, acc[0], acc[1]); fma_bf16x2(a.y, b.y, acc[2], acc[3]);
+        } else if constexpr (V == 2) {
+            fma_bf16x2(a, b, acc[0], acc[1]);
+        } else {
+            acc[0] = fmaf(__uint_as_float(static_cast<uint32_t>(a) << 16), __uint_as_float(static_cast<uint32_t>(b) << 16), acc[0]);
+        }
+    }
     static __device__ __forceinline__ void load(const bf16_t* p, float (&f)[V]) {
         if constexpr (V == 8) {
             uint4 q = ld_stream(reinterpret_cast<const uint4*>(p));
@@ -171,6 +216,13 @@ template <int V> struct VecIO<bf16_t, V> {
             f[0] = __uint_as_float(static_cast<uint32_t>(ld_stream(p)) << 16);
         }
     }
+    static __device__ __forceinline__ Raw pack(const float (&f)[V]) {      // round-to-nearest-even to storage
+        if constexpr (V == 8) return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+        else if constexpr (V == 4) return make_uint2(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]));
+        else if constexpr (V == 2) return pack_bf16x2(f[0], f[1]);
+        else return pack_bf16(f[0]);
+    }
+    static __device__ __forceinline__ void store_raw(bf16_t* p, const Raw& r) { st_stream(reinterpret_cast<Raw*>(p), r); }
     static __device__ __forceinline__ void store(bf16_t* p, const float (&f)[V]) {
         if constexpr (V == 8) {
             st_stream(reinterpret_cast<uint4*>(p), make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),

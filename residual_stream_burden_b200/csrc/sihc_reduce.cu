@@ -67,15 +67,8 @@ __global__ void __launch_bounds__(kMaxThreads) wgrad_kernel(const __grid_constan
             for (int i = 0; i < TT; ++i) {
 #pragma unroll
                 for (int s = 0; s < S; ++s) {
-                    float xv[V];
-                    IO::unpack(xr[i][s], xv);
 #pragma unroll
-                    for (int j = 0; j < EC; ++j) {
-                        float zv[V];
-                        IO::unpack(zr[j][i], zv);
-#pragma unroll
-                        for (int v = 0; v < V; ++v) acc[j * S + s][v] = fmaf(xv[v], zv[v], acc[j * S + s][v]);
-                    }
+                    for (int j = 0; j < EC; ++j) IO::fma_raw(xr[i][s], zr[j][i], acc[j * S + s]);
                 }
             }
         }
@@ -219,6 +212,7 @@ __global__ void __launch_bounds__(kMaxThreads) tri_bwd_kernel(const __grid_const
         const W* __restrict__ gamma = static_cast<const W*>(p.gamma) + ln.c0;
         const uint32_t per_tile = t.tl * TT;
         for (uint32_t tile = blockIdx.x; tile < t.ntiles; tile += gridDim.x) {
+            typename VecIO<T, V>::Raw gr[TT];
             float gv[TT][V];
             size_t off[TT];
             bool ok[TT];
@@ -227,11 +221,7 @@ __global__ void __launch_bounds__(kMaxThreads) tri_bwd_kernel(const __grid_const
                 const uint32_t m = tile * per_tile + i * t.tl + ln.tl;
                 ok[i] = m < t.M;
                 off[i] = static_cast<size_t>(ok[i] ? m : 0u) * t.C;
-                if (ok[i]) VecIO<T, V>::load(grad + off[i], gv[i]);
-                else {
-#pragma unroll
-                    for (int v = 0; v < V; ++v) gv[i][v] = 0.f;
-                }
+                gr[i] = ok[i] ? VecIO<T, V>::load_raw(grad + off[i]) : VecIO<T, V>::zero_raw();
             }
             // issue every update load of the chunk before the first use (JC*TT vectors in flight)
             typename VecIO<T, V>::Raw dr[JC][TT];
@@ -245,16 +235,13 @@ __global__ void __launch_bounds__(kMaxThreads) tri_bwd_kernel(const __grid_const
                     dr[j][i] = (have && ok[i]) ? VecIO<T, V>::load_raw(dz + off[i]) : VecIO<T, V>::zero_raw();
             }
 #pragma unroll
+            for (int i = 0; i < TT; ++i) VecIO<T, V>::unpack(gr[i], gv[i]);     // for the ddz products
+#pragma unroll
             for (int j = 0; j < JC; ++j) {
                 const int l = e0 + j;
                 if (l < e1) {
 #pragma unroll
-                    for (int i = 0; i < TT; ++i) {
-                        float d[V];
-                        VecIO<T, V>::unpack(dr[j][i], d);
-#pragma unroll
-                        for (int v = 0; v < V; ++v) acc[j][v] = fmaf(gv[i][v], d[v], acc[j][v]);
-                    }
+                    for (int i = 0; i < TT; ++i) VecIO<T, V>::fma_raw(gr[i], dr[j][i], acc[j]);
                     if (p.has_ddz && p.ddz.p[l] != nullptr) {
                         T* __restrict__ ddz = static_cast<T*>(p.ddz.p[l]) + ln.c0;
                         float gm[1][V];

@@ -207,6 +207,13 @@ __global__ void __launch_bounds__(kMaxThreads) write_read_kernel(const __grid_co
     float wb[S][V], wa[S][V];
     load_coeffs<W, S, V>(static_cast<const W*>(p.beta) + static_cast<size_t>(ln.c0) * S, wb);
     load_coeffs<W, S, V>(static_cast<const W*>(p.alpha) + static_cast<size_t>(ln.c0) * S, wa);
+    // Same-type coefficients are kept packed per slot (half the registers) and fed to the mixed-precision FMA.
+    constexpr bool kPacked = std::is_same<T, W>::value;
+    Raw wbr[kPacked ? S : 1], war[kPacked ? S : 1];
+    if constexpr (kPacked) {
+#pragma unroll
+        for (int s = 0; s < S; ++s) { wbr[s] = IO::pack(wb[s]); war[s] = IO::pack(wa[s]); }    // exact: the values are storage values
+    }
     const uint32_t per_tile = t.tl * TT;
     for (uint32_t tile = blockIdx.x; tile < t.ntiles; tile += gridDim.x) {
         Raw xr[TT][S];
@@ -221,6 +228,25 @@ __global__ void __launch_bounds__(kMaxThreads) write_read_kernel(const __grid_co
             dr[i] = ok ? IO::load_raw(dz + static_cast<size_t>(m[i]) * t.C) : IO::zero_raw();
 #pragma unroll
             for (int s = 0; s < S; ++s) xr[i][s] = ok ? IO::load_raw(x + origin[i] + slot_offset<S>(s, t.g, t.C)) : IO::zero_raw();
+        }
+        if constexpr (kPacked) {
+#pragma unroll
+            for (int i = 0; i < TT; ++i) {
+                float acc[V];
+#pragma unroll
+                for (int v = 0; v < V; ++v) acc[v] = 0.f;
+#pragma unroll
+                for (int s = 0; s < S; ++s) {
+                    float r[V];
+                    IO::unpack(xr[i][s], r);
+                    IO::fma_raw(wbr[s], dr[i], r);              // x + beta * dz
+                    const Raw yr = IO::pack(r);                 // rounded to storage: what the read sees
+                    if (m[i] < t.M) IO::store_raw(y + origin[i] + slot_offset<S>(s, t.g, t.C), yr);
+                    IO::fma_raw(yr, war[s], acc);
+                }
+                if (m[i] < t.M) IO::store(z + static_cast<size_t>(m[i]) * t.C, acc);
+            }
+            continue;
         }
 #pragma unroll
         for (int i = 0; i < TT; ++i) {
@@ -436,10 +462,18 @@ cudaError_t launch_write_read(const Problem& pb, const void* x, const void* dz, 
         return dispatch_slots(pb.S, [&](auto s_) {
             constexpr int S = decltype(s_)::value;
             constexpr int VM = VecWidth<T, S>::value;
-            // 512 threads x 2 tokens measured best on B200 (n=4, width 768: 5876 GB/s vs 5149 at 384 x 1)
             if (pb.V == 1) return launch_persistent(write_read_kernel<T, W, S, 1, 1>, p, pb, 1, 1, 512, 1, false, nullptr);
-            if (pick_tt(2) >= 2) return launch_persistent(write_read_kernel<T, W, S, VM, 2>, p, pb, VM, 2, 512, 1, false, nullptr);
-            return launch_persistent(write_read_kernel<T, W, S, VM, 1>, p, pb, VM, 1, 512, 1, false, nullptr);
+            // Block size x tokens per thread, measured on B200 (bf16, width 768, 65 536 / 524 288 tokens).  With packed
+            // same-type coefficients: n=4 256 x 1 (6313 / 6413 GB/s; 512 x 2: 5657 / 5897), n=2 384 x 2 (6114 / 6433),
+            // n=8 512 x 2 (5874 / 5933), n=16 512 x 1 (5046 / 4791).  Unpacked coefficients: 512 x 2.
+            int threads = 512, tt = 2;
+            if constexpr (std::is_same<T, W>::value) {
+                if (S == 4) { threads = 256; tt = 1; }
+                else if (S == 2) { threads = 384; tt = 2; }
+                else if (S == 16) { threads = 512; tt = 1; }
+            }
+            if (pick_tt(tt) >= 2) return launch_persistent(write_read_kernel<T, W, S, VM, 2>, p, pb, VM, 2, threads, 1, false, nullptr);
+            return launch_persistent(write_read_kernel<T, W, S, VM, 1>, p, pb, VM, 1, threads, 1, false, nullptr);
         });
     });
 }

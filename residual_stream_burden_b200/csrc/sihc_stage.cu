@@ -77,16 +77,29 @@ __global__ void __launch_bounds__(384) read_fwd_stage_kernel(const __grid_consta
             if (p.out.p[l] == nullptr) continue;      // output not wanted
             T* __restrict__ out = static_cast<T*>(p.out.p[l]) + ln.c0;
             float acc[TT][V];
+            if constexpr (std::is_same<T, W>::value) {      // packed operands straight into the accumulating FMA
 #pragma unroll
-            for (int s = 0; s < S; ++s) {
-                float w[V];
-                smem_coeffs<W, V>(wme + (static_cast<uint32_t>(l) * S + s) * CS, w);
+                for (int i = 0; i < TT; ++i)
 #pragma unroll
-                for (int i = 0; i < TT; ++i) {
-                    float xv[V];
-                    IO::unpack(xr[i][s], xv);
+                    for (int v = 0; v < V; ++v) acc[i][v] = 0.f;
 #pragma unroll
-                    for (int v = 0; v < V; ++v) acc[i][v] = s == 0 ? xv[v] * w[v] : fmaf(xv[v], w[v], acc[i][v]);
+                for (int s = 0; s < S; ++s) {
+                    const Raw wr = *reinterpret_cast<const Raw*>(wme + (static_cast<uint32_t>(l) * S + s) * CS);
+#pragma unroll
+                    for (int i = 0; i < TT; ++i) IO::fma_raw(xr[i][s], wr, acc[i]);
+                }
+            } else {
+#pragma unroll
+                for (int s = 0; s < S; ++s) {
+                    float w[V];
+                    smem_coeffs<W, V>(wme + (static_cast<uint32_t>(l) * S + s) * CS, w);
+#pragma unroll
+                    for (int i = 0; i < TT; ++i) {
+                        float xv[V];
+                        IO::unpack(xr[i][s], xv);
+#pragma unroll
+                        for (int v = 0; v < V; ++v) acc[i][v] = s == 0 ? xv[v] * w[v] : fmaf(xv[v], w[v], acc[i][v]);
+                    }
                 }
             }
 #pragma unroll
@@ -147,17 +160,26 @@ __global__ void __launch_bounds__(384) write_fwd_stage_kernel(const __grid_const
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 if (!have[k]) continue;
-                float d[TT][V];
+                if constexpr (std::is_same<T, W>::value) {
 #pragma unroll
-                for (int i = 0; i < TT; ++i) IO::unpack(dr[k][i], d[i]);
+                    for (int s = 0; s < S; ++s) {
+                        const Raw wr = *reinterpret_cast<const Raw*>(wme + (static_cast<uint32_t>(l0 + k) * S + s) * CS);
 #pragma unroll
-                for (int s = 0; s < S; ++s) {
-                    float w[V];
-                    smem_coeffs<W, V>(wme + (static_cast<uint32_t>(l0 + k) * S + s) * CS, w);
+                        for (int i = 0; i < TT; ++i) IO::fma_raw(wr, dr[k][i], acc[i][s]);
+                    }
+                } else {
+                    float d[TT][V];
 #pragma unroll
-                    for (int i = 0; i < TT; ++i)
+                    for (int i = 0; i < TT; ++i) IO::unpack(dr[k][i], d[i]);
 #pragma unroll
-                        for (int v = 0; v < V; ++v) acc[i][s][v] = fmaf(w[v], d[i][v], acc[i][s][v]);
+                    for (int s = 0; s < S; ++s) {
+                        float w[V];
+                        smem_coeffs<W, V>(wme + (static_cast<uint32_t>(l0 + k) * S + s) * CS, w);
+#pragma unroll
+                        for (int i = 0; i < TT; ++i)
+#pragma unroll
+                            for (int v = 0; v < V; ++v) acc[i][s][v] = fmaf(w[v], d[i][v], acc[i][s][v]);
+                    }
                 }
             }
         }

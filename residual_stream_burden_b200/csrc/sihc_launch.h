@@ -20,7 +20,7 @@ struct Tuning {
     int maxvec_bytes = 0;   // cap on the vector width in bytes (0: 16)
     int ring = -1;          // stages of the async-copy ring in the fused single-event adjoints (-1: default, 0: off)
     int min_block_tokens = 0;   // fewest tokens a partial-sum block should own (0: default)
-    int stage_budget_kb = 0;    // shared-memory budget of the staged-coefficient kernels in KB (0: default 50)
+    int stage_budget_kb = 0;    // shared-memory budget of the staged-coefficient kernels in KB (0: default 35)
     int tri_chunk = 0;          // events per z-slice of the triangular backward (0: default)
     int stage_smem = -1;        // stage read/write coefficients: 1 staged in shared memory, 0 re-read from L1,
                                 // -1 default (staged whenever the vector path applies)

@@ -8,10 +8,10 @@
 // global memory (`alpha.transpose(1, 2).contiguous()`, sihc/models/sihc/sublayer_kernels.py:224); this
 // library allocates nothing, so the transpose lives in shared memory.
 //
-// The slice is kept to ~50 KB (a narrower channel tile, more blocks per SM): these kernels are latency-bound, and
-// residency matters more than a wide tile.  Measured on B200 (bf16, width 768, against re-reading from L1):
-// 4 slots E=24 read 4599 -> 5074 GB/s, write 3945 -> 4517; 16 slots E=12 read 2347 -> 2938, write 2134 -> 2649.
-// With a 160 KB slice (one block per SM) the 4-slot case was slower than the L1 form (4118 / 3761).
+// The slice is kept small (at most 35 KB and 32 channel lanes per block, more blocks per SM): residency matters more
+// than a wide tile.  Measured on B200 (bf16, width 768, against re-reading the coefficients from L1): 4 slots E=24
+// read 4599 -> 5074 GB/s, write 3945 -> 4517; 16 slots E=12 read 2347 -> 2938, write 2134 -> 2649.  With a 160 KB slice
+// (one block per SM) the 4-slot case was slower than the L1 form (4118 / 3761).
 #include "sihc_dispatch.cuh"
 
 namespace sihc {
@@ -195,18 +195,22 @@ __global__ void __launch_bounds__(384) write_fwd_stage_kernel(const __grid_const
 
 namespace {
 
-// Block shape whose coefficient slice (E*S*cl*V elements of W) fits the shared-memory budget, with the channel
-// dimension split evenly over blockIdx.y.
+// Block shape: 32, 16 or 8 channel lanes (a warp then covers whole token rows), the most whose coefficient slice
+// (E*S*V elements of W per lane) fits the shared-memory budget, preferring a count that divides the channel vectors
+// evenly over blockIdx.y.  Measured on B200 (bf16, read / write GB/s): width 1152, E=24, 8192 tokens: 29 lanes
+// 3081 / 4050, 16 lanes 4409 / 4535; width 768, E=8, 65 536 tokens: 96 lanes 4960 / 5599, 32 lanes 5326 / 5943.
 struct StageShape { uint32_t cl, tl, gy, threads; size_t smem; };
 inline StageShape stage_shape(uint32_t ncv, int E, int S, int V, size_t wbytes, int target_threads) {
-    const size_t kBudget = static_cast<size_t>(tuning().stage_budget_kb > 0 ? tuning().stage_budget_kb : 50) * 1024;
+    const size_t kBudget = static_cast<size_t>(tuning().stage_budget_kb > 0 ? tuning().stage_budget_kb : 35) * 1024;
     const size_t per_lane = static_cast<size_t>(E) * S * V * wbytes;
-    uint32_t max_cl = static_cast<uint32_t>(kBudget / per_lane);
-    if (max_cl < 8) max_cl = 8;
-    if (max_cl > 384) max_cl = 384;
+    uint32_t cl = 32;
+    while (cl > 8 && per_lane * cl > kBudget) cl >>= 1;
+    for (uint32_t c = cl; c >= 8; c >>= 1)
+        if (ncv % c == 0) { cl = c; break; }
+    if (cl > ncv) cl = ncv;
     StageShape sh;
-    sh.gy = (ncv + max_cl - 1) / max_cl;
-    sh.cl = (ncv + sh.gy - 1) / sh.gy;
+    sh.cl = cl;
+    sh.gy = (ncv + cl - 1) / cl;
     uint32_t tl = (static_cast<uint32_t>(target_threads) + sh.cl / 2) / sh.cl;
     if (tl < 1) tl = 1;
     while (tl > 1 && tl * sh.cl > 384u) --tl;

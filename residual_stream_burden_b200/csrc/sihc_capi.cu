@@ -81,6 +81,16 @@ namespace {
 // (2^20 tokens, width 768 and 1152, bf16): three stages win everywhere they win at all; deeper rings lose
 // DRAM locality.  read bwd: n=4 6447 vs 6416 GB/s (width 1152: 6436 vs 6215), n=8 6194 vs 5347, n=2 loses.
 // write bwd: n=4 6710 vs 5879, n=8 6608 vs 5849, n=2 6789 (4 stages) vs 6714.
+// Stage weight gradient.  The block-tiled kernel reads the carrier once instead of once per two events (through L2)
+// and wins where the events are many; measured on B200, bf16, 4 slots, per-thread -> tiled GB/s: E=24 width 768
+// 3906 -> 4487, E=16 width 1152 3774 -> 4480; but E=12 4329 -> 3568, E=8 4836 -> 4307, and 2 / 8 / 16 slots at E=12
+// 5875 -> 2870, 2334 -> 2205, 1393 -> 1031.  wgrad_tiled = 1 / 0 forces one form on the vector path.
+inline cudaError_t stage_wgrad(const Problem& pb, const void* carrier, const void* const* z, float* partial, uint32_t* blocks) {
+    const int forced = tuning().wgrad_tiled;
+    const bool tiled = forced >= 0 ? forced != 0 : (pb.S == 4 && pb.E >= 16);
+    if (pb.V > 1 && tiled) return launch_wgrad_tiled(pb, carrier, z, partial, blocks);
+    return launch_wgrad(pb, carrier, z, partial, blocks);
+}
 inline int read_bwd_ring_stages(int S) { const int t = tuning().ring; return t >= 0 ? t : (S >= 4 ? 3 : 0); }
 inline int write_bwd_ring_stages(int S) { const int t = tuning().ring; return t >= 0 ? t : (S >= 4 ? 3 : 4); }
 constexpr int kReadBwdRingThreads = 256, kWriteBwdRingThreads = 384;
@@ -193,6 +203,7 @@ int sihc_tune(const char* name, int value) {
     else if (!std::strcmp(name, "min_block_tokens")) t.min_block_tokens = value;
     else if (!std::strcmp(name, "stage_budget_kb")) t.stage_budget_kb = value;
     else if (!std::strcmp(name, "tri_chunk")) t.tri_chunk = value;
+    else if (!std::strcmp(name, "wgrad_tiled")) t.wgrad_tiled = value;
     else if (!std::strcmp(name, "stage_smem")) t.stage_smem = value;
     else if (!std::strcmp(name, "stage_smem_default")) t.stage_smem = -1;
     else return SIHC_ERR_NULL;
@@ -285,7 +296,7 @@ int sihc_read_bwd(const void* x, const void* const* g, const void* alpha, void* 
     } else {
         e = cudaSuccess;
         if (dx) e = launch_write_fwd(pb, nullptr, g, alpha, dx);
-        if (e == cudaSuccess && dalpha) e = launch_wgrad(pb, x, g, partial, &blocks);
+        if (e == cudaSuccess && dalpha) e = stage_wgrad(pb, x, g, partial, &blocks);
     }
     if (e == cudaSuccess && dalpha)
         e = launch_finish(partial, dalpha, blocks, static_cast<uint32_t>(events) * pb.S, pb.C, pb.S, pb.stream);
@@ -326,7 +337,7 @@ int sihc_write_bwd(const void* h, const void* const* dz, const void* beta, void*
     } else {
         e = cudaSuccess;
         if (want_ddz) e = launch_read_fwd(pb, h, beta, ddz);
-        if (e == cudaSuccess && dbeta) e = launch_wgrad(pb, h, dz, partial, &blocks);
+        if (e == cudaSuccess && dbeta) e = stage_wgrad(pb, h, dz, partial, &blocks);
     }
     if (e == cudaSuccess && dbeta)
         e = launch_finish(partial, dbeta, blocks, static_cast<uint32_t>(events) * pb.S, pb.C, pb.S, pb.stream);

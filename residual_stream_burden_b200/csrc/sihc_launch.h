@@ -22,6 +22,7 @@ struct Tuning {
     int min_block_tokens = 0;   // fewest tokens a partial-sum block should own (0: default)
     int stage_budget_kb = 0;    // shared-memory budget of the staged-coefficient kernels in KB (0: default 35)
     int tri_chunk = 0;          // events per z-slice of the triangular backward (0: default)
+    int wgrad_tiled = -1;       // stage weight gradient: 1 block-tiled kernel, 0 per-thread kernel (-1: default)
     int stage_smem = -1;        // stage read/write coefficients: 1 staged in shared memory, 0 re-read from L1,
                                 // -1 default (staged whenever the vector path applies)
 };
@@ -66,6 +67,16 @@ struct WriteReadParams { const void* x; const void* dz; const void* beta; const 
 struct ReadBwd1Params { const void* x; const void* g; const void* w; void* dx; float* partial; Tiling t; };
 struct WriteBwd1Params { const void* h; const void* dz; const void* w; void* ddz; float* partial; Tiling t; };
 // Multi-event weight gradient partials: [P][E][S][C].
+struct WGradParams { const void* x; ConstPtrs z; float* partial; int E; Tiling t; };
+// Events handled per pass over the carrier by the stage weight-gradient kernel.
+template <int S, int V> struct EventChunk {
+    static constexpr int raw = 64 / (S * V);
+    static constexpr int value = raw < 1 ? 1 : (raw > 8 ? 8 : raw);
+};
+// The same partials from a block-tiled kernel: the carrier tile is staged once per block in shared memory and shared by
+// the threads that own different events (sihc_wgrad.cu).  Vector path only.
+cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const void* const* z, float* partial,
+                               uint32_t* blocks);
 cudaError_t launch_wgrad(const Problem& pb, const void* carrier, const void* const* z, float* partial,
                          uint32_t* blocks);
 // out[(row / S) * C * S + c * S + row % S] = sum_p partial[(p * rows + row) * C + c]

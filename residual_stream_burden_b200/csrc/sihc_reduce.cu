@@ -10,16 +10,9 @@
 
 namespace sihc {
 
-struct WGradParams { const void* x; ConstPtrs z; float* partial; int E; Tiling t; };
 struct TriFwdParams { const void* base; ConstPtrs dz; const void* gamma; void* out; int J; Tiling t; };
 struct TriBwdParams { const void* grad; ConstPtrs dz; const void* gamma; MutPtrs ddz; int has_ddz; float* partial; int J; int chunk; Tiling t; };
 
-
-// Events handled per pass over the carrier by the stage weight-gradient kernel.
-template <int S, int V> struct EventChunk {
-    static constexpr int raw = 64 / (S * V);
-    static constexpr int value = raw < 1 ? 1 : (raw > 8 ? 8 : raw);
-};
 
 // ---- stage weight gradient ---------------------------------------------------------------------
 // partial[block][l][s][c] = sum_{m in block} X[m,s,c] * Z_l[m,c]   for the EC events of blockIdx.z

@@ -1,0 +1,161 @@
+// Stage weight gradient, block-tiled:  partial[block][l][s][c] = sum_{m in block} X[m,s,c] * Z_l[m,c].
+//
+// `wgrad_kernel` (sihc_reduce.cu) gives each thread EC events and lets the grid's z-slices re-read the carrier once per
+// EC events; those re-reads are L2 hits, but at 24 events they are 12 passes over the carrier through L2.  Here a block
+// owns a channel slice (CL lanes of V channels) and ALL events: thread (lane, group) accumulates the EC events of its
+// group for its lane's channels over every token the block visits.  The carrier tile of a few tokens is copied once
+// per block into shared memory (`cp.async`, NST stages) and read by every event group; each thread's own Z vectors
+// travel through private ring slots.  Global traffic is S + E units, and since a (lane, group) pair is unique in the
+// block its accumulators ARE the block's partial sums: no block reduction.
+// (reference: `_weight_grad`, sihc/models/sihc/sublayer_kernels.py:130-145; a null Z_l leaves zeros, :283)
+#include "sihc_dispatch.cuh"
+#include "sihc_ring.cuh"
+
+namespace sihc {
+
+constexpr int kWGradTileThreads = 384;
+constexpr int kWGradTileTokens = 4;      // tokens per stage
+constexpr int kWGradTileStages = 3;
+
+template <typename T, int S, int V>
+__global__ void __launch_bounds__(kWGradTileThreads) wgrad_tiled_kernel(const __grid_constant__ WGradParams p) {
+    constexpr int EC = EventChunk<S, V>::value;
+    constexpr int TK = kWGradTileTokens, NST = kWGradTileStages;
+    typedef VecIO<T, V> IO;
+    typedef typename IO::Raw Raw;
+    constexpr int VB = int(sizeof(Raw));
+    extern __shared__ __align__(16) unsigned char tile_bytes[];
+    const Tiling& t = p.t;                       // t.cl channel lanes x t.tl event groups
+    const Lane ln = make_lane<V>(t);             // ln.tl = event group
+    const uint32_t CL = t.cl, nthreads = blockDim.x, tid = threadIdx.x;
+    Raw* xs = reinterpret_cast<Raw*>(tile_bytes);                              // [NST][TK][S][CL]
+    Raw* zs = xs + static_cast<size_t>(NST) * TK * S * CL;                     // [NST][TK * EC][nthreads], private slots
+    const int e0 = static_cast<int>(ln.tl) * EC;
+    const T* __restrict__ x = static_cast<const T*>(p.x);
+    const uint32_t slice_c0 = blockIdx.y * CL * V;                             // first channel of the block's slice
+    const uint32_t tile_vecs = TK * S * CL;
+
+    auto issue = [&](uint32_t tile, int stage) {
+        const bool live = tile < t.ntiles;
+        // carrier tile: every thread copies its share of the TK*S*CL vectors
+        for (uint32_t idx = tid; idx < tile_vecs; idx += nthreads) {
+            const uint32_t lane = idx % CL, r = idx / CL, s = r % S, tok = r / S;
+            const uint32_t m = tile * TK + tok;
+            const bool ok = live && m < t.M && blockIdx.y * CL + lane < t.ncv;
+            const T* src = x;
+            if (ok) src = x + cell_origin<S>(m, t.g, t.C) + slot_offset<S>(static_cast<int>(s), t.g, t.C) + slice_c0 + lane * V;
+            cp_async<VB>(xs + static_cast<size_t>(stage) * tile_vecs + idx, src, ok);
+        }
+        // this thread's own Z vectors
+#pragma unroll
+        for (int j = 0; j < EC; ++j) {
+            const int l = e0 + j;
+            const T* zl = (ln.active && l < p.E) ? static_cast<const T*>(p.z.p[l < p.E ? l : 0]) : nullptr;
+#pragma unroll
+            for (int tok = 0; tok < TK; ++tok) {
+                const uint32_t m = tile * TK + tok;
+                const bool ok = live && zl != nullptr && m < t.M;
+                cp_async<VB>(zs + (static_cast<size_t>(stage) * TK * EC + tok * EC + j) * nthreads + tid,
+                             ok ? zl + static_cast<size_t>(m) * t.C + ln.c0 : x, ok);
+            }
+        }
+        cp_async_commit();
+    };
+
+    float acc[EC * S][V];
+#pragma unroll
+    for (int a = 0; a < EC * S; ++a)
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[a][v] = 0.f;
+
+    uint32_t tile = blockIdx.x;
+#pragma unroll
+    for (int st = 0; st < NST - 1; ++st) issue(tile + st * gridDim.x, st);
+    int stage = 0;
+    for (; tile < t.ntiles; tile += gridDim.x) {
+        cp_async_wait<NST - 2>();          // this thread's copies for the tile have landed
+        __syncthreads();                   // ... and everyone else's; all threads are also done with the previous tile
+        issue(tile + (NST - 1) * gridDim.x, stage == 0 ? NST - 1 : stage - 1);
+        const Raw* xt = xs + static_cast<size_t>(stage) * tile_vecs + ln.cl;
+        const Raw* zt = zs + static_cast<size_t>(stage) * TK * EC * nthreads + tid;
+#pragma unroll
+        for (int tok = 0; tok < TK; ++tok) {
+            Raw zr[EC];
+#pragma unroll
+            for (int j = 0; j < EC; ++j) zr[j] = zt[static_cast<size_t>(tok * EC + j) * nthreads];
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                const Raw xr = xt[static_cast<size_t>(tok * S + s) * CL];
+#pragma unroll
+                for (int j = 0; j < EC; ++j) IO::fma_raw(xr, zr[j], acc[j * S + s]);
+            }
+        }
+        stage = stage + 1 == NST ? 0 : stage + 1;
+    }
+    cp_async_wait<0>();
+    if (!ln.active) return;
+    const uint32_t rows_total = static_cast<uint32_t>(p.E) * S;
+    float* dst = p.partial + static_cast<size_t>(blockIdx.x) * rows_total * t.C + ln.c0;
+#pragma unroll
+    for (int j = 0; j < EC; ++j) {
+        if (e0 + j >= p.E) break;
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+            float* d = dst + (static_cast<size_t>(e0 + j) * S + s) * t.C;
+#pragma unroll
+            for (int v = 0; v < V; ++v) d[v] = acc[j * S + s][v];
+        }
+    }
+}
+
+cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const void* const* z, float* partial,
+                               uint32_t* blocks) {
+    WGradParams p{};
+    p.x = carrier; p.partial = partial; p.E = pb.E;
+    for (int l = 0; l < pb.E; ++l) p.z.p[l] = z[l];
+    return dispatch_types(pb.dtype, pb.dtype, [&](auto tt_, auto) {
+        using T = decltype(tt_);
+        return dispatch_slots(pb.S, [&](auto s_) {
+            constexpr int S = decltype(s_)::value;
+            constexpr int V = VecWidth<T, S>::value;
+            constexpr int EC = EventChunk<S, V>::value;
+            if constexpr (V * int(sizeof(T)) < 4) return cudaErrorInvalidValue;
+            else {
+                auto kernel = wgrad_tiled_kernel<T, S, V>;
+                const uint32_t ncv = pb.C / V;
+                const uint32_t groups = static_cast<uint32_t>((pb.E + EC - 1) / EC);
+                // channel lanes: what 384 threads and 200 KB of shared memory leave per event group, split evenly over
+                // blockIdx.y (a lane costs NST*TK vectors for each of its S carrier slots and EC*groups event slots)
+                constexpr size_t kMaxDynamic = 200 * 1024;
+                const size_t vb = static_cast<size_t>(V) * sizeof(T);
+                const size_t per_lane = kWGradTileStages * kWGradTileTokens * vb * (static_cast<size_t>(S) + static_cast<size_t>(EC) * groups);
+                uint32_t max_cl = kWGradTileThreads / groups;
+                if (max_cl > kMaxDynamic / per_lane) max_cl = static_cast<uint32_t>(kMaxDynamic / per_lane);
+                if (max_cl < 1) return cudaErrorInvalidConfiguration;
+                const uint32_t gy = (ncv + max_cl - 1) / max_cl;
+                const uint32_t cl = (ncv + gy - 1) / gy;
+                const uint32_t threads = cl * groups;
+                const size_t smem = per_lane * cl;
+                if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kMaxDynamic)) return e;
+                Tiling& t = p.t;
+                t.M = pb.M; t.g = pb.g; t.C = pb.C; t.ncv = ncv; t.cl = cl; t.tl = groups;
+                t.ntiles = (pb.M + kWGradTileTokens - 1) / kWGradTileTokens;
+                int nb = cached_occupancy(reinterpret_cast<const void*>(kernel), static_cast<int>(threads), smem);
+                const int cap = tuning().rbps > 0 ? tuning().rbps : 2;
+                if (nb > cap) nb = cap;
+                if (nb < 1) nb = 1;
+                uint32_t gx = static_cast<uint32_t>(sm_count()) * static_cast<uint32_t>(nb) / gy;
+                const uint32_t bound = partial_blocks_bound(pb.M);
+                if (gx > bound) gx = bound;
+                if (gx < 1) gx = 1;
+                if (gx > t.ntiles) gx = t.ntiles;
+                if (blocks) *blocks = gx;
+                kernel<<<dim3(gx, gy, 1), threads, smem, pb.stream>>>(p);
+                count_launch();
+                return cudaGetLastError();
+            }
+        });
+    });
+}
+
+}  // namespace sihc

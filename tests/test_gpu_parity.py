@@ -397,6 +397,41 @@ def test_single_event_adjoints_register_and_ring_variants(R, stages, slots, dtyp
     close(got["dbeta"], odb.to(dtype), dtype, "dbeta")
 
 
+@pytest.mark.parametrize("tiled", [0, 1])
+@pytest.mark.parametrize("slots,b,g,c,events,dtype", [(4, 3, 7, 768, 24, torch.bfloat16), (4, 2, 5, 1152, 16, torch.bfloat16),
+                                                      (4, 2, 6, 64, 5, torch.float32), (2, 3, 5, 128, 8, torch.bfloat16),
+                                                      (8, 2, 4, 256, 12, torch.bfloat16), (16, 2, 3, 64, 12, torch.bfloat16),
+                                                      (4, 1, 3, 40, 3, torch.bfloat16)])
+def test_stage_weight_gradient_tiled_and_per_thread_forms(R, tiled, slots, b, g, c, events, dtype):
+    """The multi-event weight gradient exists as a block-tiled kernel (carrier tile shared through shared memory)
+    and as a per-thread kernel; both must match the fp64 oracle, with unused read outputs left at exactly zero."""
+    from residual_stream_burden_b200 import _lib
+    torch.manual_seed(812 + slots + events)
+    kh, kw = O.cell_shape(slots)
+    x = torch.randn(b, g * kh, g * kw, c).to(dtype)
+    alpha = (1.0 / slots + 0.05 * torch.randn(events, c, slots)).to(dtype)
+    dz = [torch.randn(b, g * g, c).to(dtype) for _ in range(events)]
+    gz = [torch.randn(b, g * g, c).to(dtype) for _ in range(events)]
+    gy = torch.randn(b, g * kh, g * kw, c).to(dtype)
+    _lib.tune("wgrad_tiled", tiled)
+    try:
+        got = run_all(R, x, alpha, alpha, dz, gz, gy)
+        holes = [t.to(DEV) if i % 3 else None for i, t in enumerate(gz)]
+        _, da_holes = R.ops._read_backward_op(x.to(DEV), holes, alpha.to(DEV), False, True)
+        torch.cuda.synchronize()
+    finally:
+        _lib.tune("wgrad_tiled", -1)
+    _, oda = O.read_backward(x, gz, alpha, acc=torch.float64)
+    _, odb = O.write_backward(gy, dz, alpha, acc=torch.float64)
+    close(got["dalpha"], oda.to(dtype), dtype, "dalpha")
+    close(got["dbeta"], odb.to(dtype), dtype, "dbeta")
+    for i in range(events):
+        if i % 3 == 0:
+            assert not da_holes[i].any()
+        else:
+            close(da_holes[i], oda[i].to(dtype), dtype, f"dalpha[{i}] with unused outputs")
+
+
 @pytest.mark.parametrize("active,c,dtype,gamma_fp32", [(3, 64, torch.bfloat16, False), (5, 768, torch.bfloat16, True),
                                                        (8, 128, torch.float32, True), (12, 1152, torch.bfloat16, False),
                                                        (23, 768, torch.bfloat16, False), (23, 64, torch.bfloat16, True)])

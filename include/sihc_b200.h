@@ -184,9 +184,17 @@ int sihc_tri_bwd(const void* grad, const void* const* dz, const void* gamma, voi
                  int64_t tokens, int channels, int dtype, int gdtype, void* stream);
 
 /*
- * Benchmark-only knob: override a launch parameter by name ("threads",
- * "tokens_per_thread", "blocks_per_sm", ...); value <= 0 restores the default.
- * Process-global and not thread-safe; never needed for correct results.
+ * Benchmark-only knob: override a launch parameter by name; never needed for
+ * correct results.  Process-global and not thread-safe.
+ *   "threads", "tokens_per_thread", "blocks_per_sm", "partial_blocks_per_sm",
+ *   "max_vector_bytes", "min_block_tokens", "stage_budget_kb" (KB of shared memory
+ *   for a block's coefficient slice), "tri_chunk" (events per grid slice of the
+ *   triangular backward, 1..8): value <= 0 restores the default.
+ *   "ring_stages" (0 = register-staged single-event adjoints, 3..8 = async-copy ring),
+ *   "stage_smem" (0 = stage coefficients from L1, 1 = from shared memory),
+ *   "wgrad_tiled" (0 = per-thread, 1 = block-tiled stage weight gradient): a negative
+ *   value restores the per-kernel default ("ring_default" / "stage_smem_default"
+ *   with any value do the same).
  * Returns 0, or SIHC_ERR_NULL for an unknown name.  (Counterpart of the
  * reference's `SIHC_*` environment tile overrides, sihc/models/sihc/kernels.py:19-23.)
  */

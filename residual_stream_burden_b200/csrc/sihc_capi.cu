@@ -192,19 +192,20 @@ const char* sihc_status_string(int status) {
 int sihc_tune(const char* name, int value) {
     if (!name) return SIHC_ERR_NULL;
     Tuning& t = tuning();
+    const int tri = value < 0 ? -1 : value;      // three-state knobs: a negative value restores the per-kernel default
     if (value < 0) value = 0;
     if (!std::strcmp(name, "threads")) t.threads = value;
     else if (!std::strcmp(name, "tokens_per_thread")) t.tt = value;
     else if (!std::strcmp(name, "blocks_per_sm")) t.bps = value;
     else if (!std::strcmp(name, "partial_blocks_per_sm")) t.rbps = value;
     else if (!std::strcmp(name, "max_vector_bytes")) t.maxvec_bytes = value;
-    else if (!std::strcmp(name, "ring_stages")) t.ring = value;          // 0 = register-staged kernels
+    else if (!std::strcmp(name, "ring_stages")) t.ring = tri;            // 0 = register-staged kernels
     else if (!std::strcmp(name, "ring_default")) t.ring = -1;            // back to the per-kernel default
     else if (!std::strcmp(name, "min_block_tokens")) t.min_block_tokens = value;
     else if (!std::strcmp(name, "stage_budget_kb")) t.stage_budget_kb = value;
     else if (!std::strcmp(name, "tri_chunk")) t.tri_chunk = value;
-    else if (!std::strcmp(name, "wgrad_tiled")) t.wgrad_tiled = value;
-    else if (!std::strcmp(name, "stage_smem")) t.stage_smem = value;
+    else if (!std::strcmp(name, "wgrad_tiled")) t.wgrad_tiled = tri;    // 1 block-tiled, 0 per-thread weight gradient
+    else if (!std::strcmp(name, "stage_smem")) t.stage_smem = tri;
     else if (!std::strcmp(name, "stage_smem_default")) t.stage_smem = -1;
     else return SIHC_ERR_NULL;
     return SIHC_OK;

@@ -133,9 +133,11 @@ int sihc_read_bwd(const void* x, const void* const* g, const void* alpha, void* 
  *   - Returns SIHC_ERR_CAPACITY, before launching anything, when
  *     sihc_wgrad_workspace_bytes(...) for the case exceeds SIHC_STATIC_SCRATCH_BYTES
  *     (single event, 4 slots, 768 channels needs 3.6 MB; the limit is 16 MiB).
- *   - The first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress, with that device current).  What the top of this header
- *     says about compiled graphs and stream capture is not stated for this entry point.
+ *   - The first call on each device does a one-time set-up: it looks up the array's
+ *     device address (cudaGetSymbolAddress, with that device current).  Make that first
+ *     call before any stream capture is started on the device.  The sentence at the top
+ *     of this header about compiled graphs and stream capture is not extended to this
+ *     entry point.
  *   - One array per device is shared by all calls: calls that can overlap on the GPU
  *     race and must be serialised by the caller.  The array keeps the previous call's
  *     partial sums; they are never read (every row is rewritten before use).

@@ -16,8 +16,9 @@
 // The array's name below is only a handle in host code, not a device address; the
 // address used by the kernels comes from cudaGetSymbolAddress, asked once per device
 // (with that device current) on the first call made on that device.  That first call
-// may also trigger the lazy loading of the module.  No call here reaches cudaMalloc,
-// cudaFree or an allocating library routine.
+// may also trigger the lazy loading of the module, so it should be made before any
+// stream capture is started on that device.  No call here reaches cudaMalloc, cudaFree
+// or an allocating library routine.
 //
 // Sharing: there is exactly one array per device.  Calls that may overlap on the
 // GPU (different streams, different host threads) race on it and must be serialised

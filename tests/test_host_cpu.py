@@ -63,3 +63,19 @@ def test_fake_kernels_trace_on_meta_device():
     g = torch.empty(3, 64, device="meta", dtype=torch.float32)
     t = R.sublayer_triangular(outs[0], outs[:3], g)
     assert t.shape == outs[0].shape
+
+
+def test_product_code_never_reaches_the_oracle_or_scratch_scripts():
+    """The package must compute on the CUDA library alone: the CPU oracle is a checker for
+    the tests, the smoke run and the benchmark's CPU legs, never a fallback."""
+    pkg = os.path.join(ROOT, "residual_stream_burden_b200")
+    pattern = re.compile(r"^\s*(from|import)\s+(oracle|_work)\b|[\"'](oracle|_work)[/\"']", re.M)
+    for folder, _, files in os.walk(pkg):
+        for name in files:
+            if name.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(folder, name)).read()
+                assert not pattern.search(text), f"{name} refers to oracle/ or _work/"
+    bench = open(os.path.join(ROOT, "bench.py")).read()
+    assert not re.search(r"(^|[^A-Za-z0-9])_work/", bench)
+    # the benchmark imports the oracle lazily, inside its CPU legs only
+    assert not re.search(r"^(from|import)\s+oracle\b", bench, re.M)

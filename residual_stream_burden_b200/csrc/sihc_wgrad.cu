@@ -13,14 +13,15 @@
 
 namespace sihc {
 
-constexpr int kWGradTileThreads = 384;
+constexpr int kWGradTileThreads = 384;        // launch bound; the `threads` knob may ask for up to this many
+constexpr int kWGradTileDefaultThreads = 192; // default target: two blocks per SM overlap each other's tile barriers
 constexpr int kWGradTileTokens = 4;      // tokens per stage
 constexpr int kWGradTileStages = 3;
 
-template <typename T, int S, int V>
+template <typename T, int S, int V, int TK>
 __global__ void __launch_bounds__(kWGradTileThreads) wgrad_tiled_kernel(const __grid_constant__ WGradParams p) {
     constexpr int EC = EventChunk<S, V>::value;
-    constexpr int TK = kWGradTileTokens, NST = kWGradTileStages;
+    constexpr int NST = kWGradTileStages;
     typedef VecIO<T, V> IO;
     typedef typename IO::Raw Raw;
     constexpr int VB = int(sizeof(Raw));
@@ -108,6 +109,15 @@ __global__ void __launch_bounds__(kWGradTileThreads) wgrad_tiled_kernel(const __
     }
 }
 
+// Tokens per stage of the carrier tile: kWGradTileTokens unless the `tokens_per_thread` knob asks for 2 or 8.
+template <typename F> cudaError_t dispatch_tile_tokens(F&& f) {
+    switch (tuning().tt) {
+        case 2: return f(std::integral_constant<int, 2>{});
+        case 8: return f(std::integral_constant<int, 8>{});
+        default: return f(std::integral_constant<int, kWGradTileTokens>{});
+    }
+}
+
 cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const void* const* z, float* partial,
                                uint32_t* blocks) {
     WGradParams p{};
@@ -120,16 +130,23 @@ cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const voi
             constexpr int V = VecWidth<T, S>::value;
             constexpr int EC = EventChunk<S, V>::value;
             if constexpr (V * int(sizeof(T)) < 4) return cudaErrorInvalidValue;
-            else {
-                auto kernel = wgrad_tiled_kernel<T, S, V>;
+            else return dispatch_tile_tokens([&](auto tk_) {
+                constexpr int TK = decltype(tk_)::value;
+                auto kernel = wgrad_tiled_kernel<T, S, V, TK>;
                 const uint32_t ncv = pb.C / V;
                 const uint32_t groups = static_cast<uint32_t>((pb.E + EC - 1) / EC);
-                // channel lanes: what 384 threads and 200 KB of shared memory leave per event group, split evenly over
-                // blockIdx.y (a lane costs NST*TK vectors for each of its S carrier slots and EC*groups event slots)
+                // channel lanes: what the block's threads and 200 KB of shared memory leave per event group, split evenly
+                // over blockIdx.y (a lane costs NST*TK vectors for each of its S carrier slots and EC*groups event slots).
+                // 192 threads = 16 lanes at 24 events: two blocks fit an SM and overlap each other's tile barriers
+                // (measured on B200, 4 slots, E=24, width 768: 384 threads 4485, 256 4489, 192 4703, 128 3247 GB/s;
+                // 2 or 8 tokens per stage instead of 4: 4221 / 3298).
                 constexpr size_t kMaxDynamic = 200 * 1024;
                 const size_t vb = static_cast<size_t>(V) * sizeof(T);
-                const size_t per_lane = kWGradTileStages * kWGradTileTokens * vb * (static_cast<size_t>(S) + static_cast<size_t>(EC) * groups);
-                uint32_t max_cl = kWGradTileThreads / groups;
+                const size_t per_lane = kWGradTileStages * TK * vb * (static_cast<size_t>(S) + static_cast<size_t>(EC) * groups);
+                uint32_t block_threads = kWGradTileDefaultThreads;
+                if (tuning().threads > 0) block_threads = static_cast<uint32_t>(tuning().threads < kWGradTileThreads ? tuning().threads : kWGradTileThreads);
+                if (block_threads < groups) block_threads = groups;
+                uint32_t max_cl = block_threads / groups;
                 if (max_cl > kMaxDynamic / per_lane) max_cl = static_cast<uint32_t>(kMaxDynamic / per_lane);
                 if (max_cl < 1) return cudaErrorInvalidConfiguration;
                 const uint32_t gy = (ncv + max_cl - 1) / max_cl;
@@ -139,7 +156,7 @@ cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const voi
                 if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kMaxDynamic)) return e;
                 Tiling& t = p.t;
                 t.M = pb.M; t.g = pb.g; t.C = pb.C; t.ncv = ncv; t.cl = cl; t.tl = groups;
-                t.ntiles = (pb.M + kWGradTileTokens - 1) / kWGradTileTokens;
+                t.ntiles = (pb.M + TK - 1) / TK;
                 int nb = cached_occupancy(reinterpret_cast<const void*>(kernel), static_cast<int>(threads), smem);
                 const int cap = tuning().rbps > 0 ? tuning().rbps : 2;
                 if (nb > cap) nb = cap;
@@ -153,7 +170,7 @@ cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const voi
                 kernel<<<dim3(gx, gy, 1), threads, smem, pb.stream>>>(p);
                 count_launch();
                 return cudaGetLastError();
-            }
+            });
         });
     });
 }

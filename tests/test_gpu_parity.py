@@ -400,7 +400,7 @@ def test_single_event_adjoints_register_and_ring_variants(R, stages, slots, dtyp
 @pytest.mark.parametrize("tiled", [0, 1])
 @pytest.mark.parametrize("slots,b,g,c,events,dtype", [(4, 3, 7, 768, 24, torch.bfloat16), (4, 2, 5, 1152, 16, torch.bfloat16),
                                                       (4, 2, 6, 64, 5, torch.float32), (2, 3, 5, 128, 8, torch.bfloat16),
-                                                      (8, 2, 4, 256, 12, torch.bfloat16), (16, 2, 3, 64, 12, torch.bfloat16),
+                                                      (8, 2, 4, 256, 12, torch.bfloat16), (8, 2, 4, 256, 24, torch.bfloat16), (16, 2, 3, 64, 12, torch.bfloat16),
                                                       (4, 1, 3, 40, 3, torch.bfloat16)])
 def test_stage_weight_gradient_tiled_and_per_thread_forms(R, tiled, slots, b, g, c, events, dtype):
     """The multi-event weight gradient exists as a block-tiled kernel (carrier tile shared through shared memory)

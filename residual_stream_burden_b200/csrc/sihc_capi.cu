@@ -84,10 +84,10 @@ namespace {
 // Stage weight gradient.  The block-tiled kernel reads the carrier once instead of once per two events (through L2)
 // and wins where the events are many; measured on B200, bf16, 4 slots, per-thread -> tiled GB/s: E=24 width 768
 // 3906 -> 4487, E=16 width 1152 3774 -> 4480; but E=12 4329 -> 3568, E=8 4836 -> 4307, and 2 / 8 / 16 slots at E=12
-// 5875 -> 2870, 2334 -> 2205, 1393 -> 1031.  With 192-thread blocks (16 channel lanes at 24 events, two blocks per SM)
-// the tiled form gives, at 65 536 tokens and width 768, E=24 4703 and E=16 4577 (per-thread 3916 / 4125); at 8192 tokens
-// and width 1152, E=24 3933 and E=16 3623 (per-thread 3191 / 3310); E=12 stays a draw (4475 vs 4333, 3142 vs 3339).
-// 8 slots at 24 events: 1922 -> 2298.  wgrad_tiled = 1 / 0 forces one form on the vector path.
+// 5875 -> 2870, 2334 -> 2205, 1393 -> 1031.  With 192-thread blocks and the tile ring shaped per event count
+// (sihc_wgrad.cu) the tiled form gives, at 65 536 tokens and width 768, E=24 5048 and E=16 4563 (per-thread 3877 /
+// 4087); at 8192 tokens and width 1152, E=24 4137 and E=16 3641 (per-thread 3147 / 3271); E=12 stays a draw (4475 vs
+// 4333, 3142 vs 3339).  8 slots at 24 events: 1906 -> 2488.  wgrad_tiled = 1 / 0 forces one form on the vector path.
 inline cudaError_t stage_wgrad(const Problem& pb, const void* carrier, const void* const* z, float* partial, uint32_t* blocks) {
     const int forced = tuning().wgrad_tiled;
     const bool tiled = forced >= 0 ? forced != 0 : ((pb.S == 4 && pb.E >= 16) || (pb.S == 8 && pb.E >= 24));

@@ -15,13 +15,12 @@ namespace sihc {
 
 constexpr int kWGradTileThreads = 384;        // launch bound; the `threads` knob may ask for up to this many
 constexpr int kWGradTileDefaultThreads = 192; // default target: two blocks per SM overlap each other's tile barriers
-constexpr int kWGradTileTokens = 4;      // tokens per stage
-constexpr int kWGradTileStages = 3;
+constexpr int kWGradTileTokens = 4;      // tokens per stage and stages of the tile ring, unless dispatch_tile_shape
+constexpr int kWGradTileStages = 3;      // picks the (8, 2) shape
 
-template <typename T, int S, int V, int TK>
+template <typename T, int S, int V, int TK, int NST>
 __global__ void __launch_bounds__(kWGradTileThreads) wgrad_tiled_kernel(const __grid_constant__ WGradParams p) {
     constexpr int EC = EventChunk<S, V>::value;
-    constexpr int NST = kWGradTileStages;
     typedef VecIO<T, V> IO;
     typedef typename IO::Raw Raw;
     constexpr int VB = int(sizeof(Raw));
@@ -109,13 +108,18 @@ __global__ void __launch_bounds__(kWGradTileThreads) wgrad_tiled_kernel(const __
     }
 }
 
-// Tokens per stage of the carrier tile: kWGradTileTokens unless the `tokens_per_thread` knob asks for 2 or 8.
-template <typename F> cudaError_t dispatch_tile_tokens(F&& f) {
-    switch (tuning().tt) {
-        case 2: return f(std::integral_constant<int, 2>{});
-        case 8: return f(std::integral_constant<int, 8>{});
-        default: return f(std::integral_constant<int, kWGradTileTokens>{});
-    }
+// Shape of the tile ring: (tokens per stage, stages).  What matters is how many tokens of copies a block keeps in
+// flight, (stages - 1) x tokens: 8 is the optimum and 16 collapses (the threads stall issuing copies into a full
+// memory queue instead of computing).  Measured on B200, bf16, 4 slots, 65 536 tokens, width 768, GB/s:
+//   24 events: (4,3) two blocks per SM 4690, (8,2) one block 5027, (8,3) 3292, (4,2) 4131, (2,3) 4201
+//   16 events: (4,3) 4569, (8,2) 3216, (4,2) 4233
+// and at 8192 tokens, width 1152: 24 events 3924 vs 4128, 16 events 3626 vs 2812; 8 slots, 24 events: 2288 vs 2490.
+// So twelve event groups take (8,2) and fewer take (4,3); the `tokens_per_thread` knob (4 or 8) forces one of them.
+template <typename F> cudaError_t dispatch_tile_shape(uint32_t groups, F&& f) {
+    const int forced = tuning().tt;
+    const bool wide = forced == 8 || (forced != kWGradTileTokens && groups >= 12);
+    if (wide) return f(std::integral_constant<int, 8>{}, std::integral_constant<int, 2>{});
+    return f(std::integral_constant<int, kWGradTileTokens>{}, std::integral_constant<int, kWGradTileStages>{});
 }
 
 cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const void* const* z, float* partial,
@@ -130,19 +134,20 @@ cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const voi
             constexpr int V = VecWidth<T, S>::value;
             constexpr int EC = EventChunk<S, V>::value;
             if constexpr (V * int(sizeof(T)) < 4) return cudaErrorInvalidValue;
-            else return dispatch_tile_tokens([&](auto tk_) {
+            else return dispatch_tile_shape(static_cast<uint32_t>((pb.E + EC - 1) / EC), [&](auto tk_, auto nst_) {
                 constexpr int TK = decltype(tk_)::value;
-                auto kernel = wgrad_tiled_kernel<T, S, V, TK>;
+                constexpr int NST = decltype(nst_)::value;
+                auto kernel = wgrad_tiled_kernel<T, S, V, TK, NST>;
                 const uint32_t ncv = pb.C / V;
                 const uint32_t groups = static_cast<uint32_t>((pb.E + EC - 1) / EC);
                 // channel lanes: what the block's threads and 200 KB of shared memory leave per event group, split evenly
                 // over blockIdx.y (a lane costs NST*TK vectors for each of its S carrier slots and EC*groups event slots).
-                // 192 threads = 16 lanes at 24 events: two blocks fit an SM and overlap each other's tile barriers
-                // (measured on B200, 4 slots, E=24, width 768: 384 threads 4485, 256 4489, 192 4703, 128 3247 GB/s;
-                // 2 or 8 tokens per stage instead of 4: 4221 / 3298).
+                // 192 threads = 16 lanes at 24 events (measured on B200, 4 slots, width 768, with three 4-token stages:
+                // 384 threads 4485, 256 4489, 192 4703, 128 3247 GB/s; with two 8-token stages: 384 4060, 256 3606,
+                // 192 5048; 16 events, three 4-token stages: 384 4404, 256 3774, 192 4563).
                 constexpr size_t kMaxDynamic = 200 * 1024;
                 const size_t vb = static_cast<size_t>(V) * sizeof(T);
-                const size_t per_lane = kWGradTileStages * TK * vb * (static_cast<size_t>(S) + static_cast<size_t>(EC) * groups);
+                const size_t per_lane = NST * TK * vb * (static_cast<size_t>(S) + static_cast<size_t>(EC) * groups);
                 uint32_t block_threads = kWGradTileDefaultThreads;
                 if (tuning().threads > 0) block_threads = static_cast<uint32_t>(tuning().threads < kWGradTileThreads ? tuning().threads : kWGradTileThreads);
                 if (block_threads < groups) block_threads = groups;

@@ -75,6 +75,23 @@ def load_peaks():
     return 6650.0, "fallback"
 
 
+def recorded_traffic_ratio(stage, slots, channels, dtype_name, library_version):
+    """(DRAM bytes / algorithmic bytes, source) for one hot-path stage from the tracked ncu record, or (None, why)."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f)
+    except (OSError, ValueError):
+        return None, "no profiles/dram_traffic.json"
+    if rec.get("library_version") != library_version:
+        return None, f"record is for library version {rec.get('library_version')}, this is {library_version}"
+    key = f"single_event/n{slots}/c{channels}/{dtype_name}"
+    entry = rec.get("cases", {}).get(key, {}).get(stage)
+    if not entry:
+        return None, f"no record for {key}/{stage}"
+    return float(entry["dram_over_algorithmic"]), f"{entry['source']} ({entry['kernel']}), scaled by tokens"
+
+
 class ClockSampler:
     """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
 
@@ -211,11 +228,12 @@ def run_e2e(args, batch, grid, slots, channels, dtype, device, steps):
     nchunks = (batch + chunk - 1) // chunk
     gen = torch.Generator().manual_seed(1)
     ibits = torch.int16 if dtype == torch.bfloat16 else torch.int32
+    # random bit patterns of positive finite values in [2^-31, 1): cheap to generate for GBs of pinned memory
+    lo, hi = (0x3000, 0x3F80) if dtype == torch.bfloat16 else (0x30000000, 0x3F800000)
 
     def host(*shape):
-        # pinned buffer filled with small finite values (random low bit patterns: cheap to generate)
         t = torch.empty(*shape, dtype=dtype).pin_memory()
-        t.view(ibits).random_(-8000, 8000, generator=gen)
+        t.view(ibits).random_(lo, hi, generator=gen)
         return t
 
     carrier, work = (chunk, grid * kh, grid * kw, channels), (chunk, grid * grid, channels)
@@ -278,6 +296,9 @@ def run_e2e(args, batch, grid, slots, channels, dtype, device, steps):
 
     step()
     torch.cuda.synchronize()
+    for out in h_out[:min(NB, nchunks)]:        # the streamed results are real numbers, not Inf/NaN patterns
+        assert all(bool(torch.isfinite(t.float()).all()) for t in out.values()), "non-finite end-to-end result"
+    assert bool(torch.isfinite(h_dw.float()).all())
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
@@ -539,8 +560,9 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         ms = time_device(step, steps, warmup, world, device)
         name = f"SiHC-XL Heun sampling, {sample_steps} steps, CFG 2.4 on [0.1,0.9], batch 256 per GPU, bf16 autocast, literal fused write+read schedule"
     name += ", torch.compile (CUDA graphs) around the torch sublayers" if compile_model else ", eager"
-    res = {"workload": name, "img_per_s": round(world * batch / (ms * 1e-3), 2), "ms_per_step": round(ms, 3),
-           "global_batch": world * batch, "routing_launches_per_step": per_step_launches,
+    res = {"workload": name, "img_per_s": round(world * batch / (ms * 1e-3), 2),
+           "img_per_s_per_gpu": round(batch / (ms * 1e-3), 2), "ms_per_step": round(ms, 3),
+           "steps": steps, "warmup": warmup, "global_batch": world * batch, "routing_launches_per_step": per_step_launches,
            "peak_mem_gb": round(torch.cuda.max_memory_allocated(device) / 2**30, 2)}
     del model
     torch.cuda.empty_cache()
@@ -656,6 +678,7 @@ def main():
             dist.destroy_process_group()
         return
 
+    from residual_stream_burden_b200.dist import allreduce_weight_grads
     inp = make_inputs(batch, grid, slots, channels, dtype, device, seed=rank)
     path = DevicePath(inp, batch, grid, slots, channels, dtype)
 
@@ -667,21 +690,24 @@ def main():
             if events is not None:
                 events[k][1].record()
         if world > 1:       # data-parallel exchange of the small weight gradients: one NCCL all-reduce
-            dist.all_reduce(path.wgrads)
-            path.wgrads.div_(world)
+            allreduce_weight_grads([path.wgrads])
 
     # The clock sampler (nvidia-smi, 100 ms period) needs a few hundred ms to deliver its first line, longer
-    # than the timed region itself, so it is started first and the same step keeps running as warm-up until it
-    # has reported at least three samples under load (bounded); its record covers warm-up + timed steps.
+    # than the timed region itself.  It is started first and the GPU is kept under the same load until it has
+    # reported three samples (bounded, single GPU only; these passes are not warm-up steps and are not counted);
+    # then come exactly W warm-up steps and K timed steps.  Its record covers all of it.
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    warm_done, t_warm = 0, time.perf_counter()
-    while warm_done < max(args.warmup, 3) or (rank == 0 and world == 1 and sampler.proc is not None
-                                               and len(sampler.samples) < 3 and time.perf_counter() - t_warm < 3.0):
+    t_wait = time.perf_counter()
+    while (rank == 0 and world == 1 and sampler.proc is not None and len(sampler.samples) < 3
+           and time.perf_counter() - t_wait < 3.0):
         step()
         torch.cuda.synchronize()
-        warm_done += 1
+    warmup = max(args.warmup, 3)           # the timing rules ask for at least three
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     per_kernel = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(4)]
@@ -717,23 +743,30 @@ def main():
     dominant = max(DevicePath.STAGES, key=lambda n: kernel_ms[n])
     dom_bytes = units[dominant] * tokens * channels * esize
     achieved = dom_bytes / (kernel_ms[dominant] * 1e-3) / 1e9
-    # DRAM traffic per launch: ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the 2^18-token case of this
-    # workload measured 0.988 x the algorithmic bytes for every kernel; traffic is proportional to tokens.
-    ncu_ratio = 0.988 if (slots, channels, args.dtype) == (4, 768, "bf16") else None
+    # DRAM traffic per launch is not measured in this run: it is the ncu figure (dram__bytes_read.sum +
+    # dram__bytes_write.sum over algorithmic bytes) recorded in profiles/dram_traffic.json for this kernel and
+    # configuration, scaled to this launch (traffic is proportional to tokens); null when the record is for
+    # another library version or configuration.
+    ncu_ratio, ncu_source = recorded_traffic_ratio(dominant, slots, channels, args.dtype, _lib.lib.sihc_version())
     roofline = {"bound": "hbm", "kernel": dominant, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "peak_source": f"{peak_kind} copy bandwidth",
                 "algorithmic_bytes_per_launch": dom_bytes,
                 "traffic": int(dom_bytes * ncu_ratio) if ncu_ratio else None,
+                "traffic_source": ncu_source,
                 "all_kernels": kernels, "step_frac_of_peak": round(value / world / peak, 4)}
 
-    # The legs below add to the headline line but must never prevent it from being printed: a failure in one of
-    # them is recorded in its place (every rank takes the same path, so collectives stay matched).
+    # The legs below add to the headline line.  On one GPU a failure in one of them is recorded in its place and
+    # the line is still printed.  With several ranks a rank-local failure (out of memory, a compile error) must
+    # not be swallowed: the other ranks would wait for it inside a collective on their GPUs, so the exception
+    # propagates, this process exits non-zero and the launcher ends the whole job at once.
     e2e = None
     if not args.no_e2e:
         try:
             sec, h2d, d2h, chunk = run_e2e(args, batch, grid, slots, channels, dtype, device, args.e2e_steps)
             err = None
         except Exception as exc:                                   # noqa: BLE001
+            if world > 1:
+                raise
             sec, h2d, d2h, chunk, err = float("inf"), 0, 0, 0, repr(exc)[:300]
         if world > 1:
             t = torch.tensor([sec], device=device)
@@ -765,14 +798,16 @@ def main():
         models = {}
         for kind in (("sihc_xl_train", "sihc_b_fwd") if world == 1 else ("sihc_xl_train",)):
             try:
-                models[kind] = model_workload(kind, device, rank, world, local_rank, 5, 3, 50, cm)
+                models[kind] = model_workload(kind, device, rank, world, local_rank, 20, 8, 50, cm)
             except Exception as exc:                               # noqa: BLE001
+                if world > 1:
+                    raise                                          # see above: never leave the peers waiting
                 models[kind] = {"error": repr(exc)[:300]}
                 torch.cuda.empty_cache()
 
     if rank == 0:
         line = {"metric": "sihc_read_write_fwd_bwd_bandwidth", "value": round(value, 1), "unit": "GB/s",
-                "n_gpus": world, "steps": args.steps, "warmup": warm_done,
+                "n_gpus": world, "steps": args.steps, "warmup": warmup,
                 "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "config": config,
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),

@@ -89,7 +89,8 @@ int sihc_write_fwd(const void* x, const void* const* dz, const void* beta, void*
  * `carrier = write_torch(carrier, [dz], [beta]); z = read_torch(carrier, alpha_next)` of the reference's
  * literal schedule (sihc/bench/fusion_controls.py:64, :80; research/tests/test_sublayer_kernels.py:216-226)
  * and gives the same values, moving 2*slots+2 elements per token and channel instead of 3*slots+2.
- * `y` may be `x` (in-place carrier update).  Forward only.
+ * `y` may be `x` (in-place carrier update: the carrier is then read with coherent loads, every element by the
+ * thread that rewrites it); any other overlap of `y` with an input is not allowed.  Forward only.
  */
 int sihc_write_read_fwd(const void* x, const void* dz, const void* beta, const void* alpha_next,
                         void* y, void* z_next, int64_t batch, int grid, int kh, int kw, int channels,
@@ -99,6 +100,10 @@ int sihc_write_read_fwd(const void* x, const void* dz, const void* beta, const v
  * Bytes of scratch the two backward entry points below need for `events` events
  * on this geometry (per-block partial sums of the weight gradients).  The
  * scratch needs no initialisation and holds nothing between calls.
+ * The size depends on the launch parameters in force ("partial_blocks_per_sm" and
+ * "min_block_tokens" of sihc_tune): size the scratch and make the call under the same
+ * settings, or the call returns SIHC_ERR_WORKSPACE.  The same holds for
+ * sihc_tri_workspace_bytes.
  */
 size_t sihc_wgrad_workspace_bytes(int events, int64_t batch, int grid, int kh, int kw,
                                   int channels, int dtype);
@@ -187,7 +192,9 @@ int sihc_tri_bwd(const void* grad, const void* const* dz, const void* gamma, voi
 
 /*
  * Benchmark-only knob: override a launch parameter by name; never needed for
- * correct results.  Process-global and not thread-safe.
+ * correct results.  Process-global and not thread-safe.  "partial_blocks_per_sm" and
+ * "min_block_tokens" change what sihc_*_workspace_bytes return: do not change them
+ * between sizing a workspace and the call that uses it.
  *   "threads", "tokens_per_thread", "blocks_per_sm", "partial_blocks_per_sm",
  *   "max_vector_bytes", "min_block_tokens", "stage_budget_kb" (KB of shared memory
  *   for a block's coefficient slice), "tri_chunk" (events per grid slice of the

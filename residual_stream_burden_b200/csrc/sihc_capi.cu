@@ -21,15 +21,15 @@ Tuning& tuning() {
 }
 
 int sm_count() {
-    static int cached[64];
+    static std::atomic<int> cached[64];     // zero-initialised; concurrent first calls all store the same value
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-    if (cached[dev] == 0) {
-        int n = 0;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
 }
 
 namespace {
@@ -125,6 +125,9 @@ int make_problem(Problem& pb, int events, int64_t batch, int grid, int kh, int k
     if (batch < 1 || grid < 1 || channels < 1) return SIHC_ERR_SHAPE;
     const int64_t tokens = batch * grid * grid;
     if (grid > 65535 || tokens >= (int64_t(1) << 31) || channels > (1 << 24)) return SIHC_ERR_SHAPE;
+    // the kernels keep a slot's offset inside its cell row block in 32 bits: (kh-1) carrier rows + one cell row
+    const int64_t slot_span = (static_cast<int64_t>(kh - 1) * grid * kw + kw) * channels;
+    if (slot_span >= (int64_t(1) << 32)) return SIHC_ERR_SHAPE;
     pb.dtype = static_cast<DType>(dtype);
     pb.wdtype = static_cast<DType>(wdtype);
     pb.E = events; pb.S = S;
@@ -182,7 +185,7 @@ const char* sihc_status_string(int status) {
         case SIHC_ERR_DTYPE: return "unsupported dtype (fp32/bf16 activations; weights in the activation dtype or fp32)";
         case SIHC_ERR_EVENTS: return "event count outside 1..24";
         case SIHC_ERR_CELL: return "unsupported slot grid (kh,kw); supported: (1,2) (2,2) (2,4) (4,4)";
-        case SIHC_ERR_SHAPE: return "batch, grid and channels must be positive and tokens must fit 31 bits";
+        case SIHC_ERR_SHAPE: return "batch, grid and channels must be positive, tokens must fit 31 bits and one cell row block 32 bits";
         case SIHC_ERR_WORKSPACE: return "workspace missing, not 16-byte aligned, or smaller than sihc_*_workspace_bytes";
         case SIHC_ERR_ALIGN: return "a tensor pointer is not aligned to its element size";
         case SIHC_ERR_CAPACITY: return "size exceeds the fixed capacity of this entry point";

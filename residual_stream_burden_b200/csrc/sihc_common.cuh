@@ -142,6 +142,8 @@ template <int V> struct VecIO<float, V> {
     static_assert(V == 1 || V == 2 || V == 4, "fp32 vector width");
     typedef typename RawBits<4 * V>::type Raw;
     static __device__ __forceinline__ Raw load_raw(const float* p) { return ld_stream(reinterpret_cast<const Raw*>(p)); }
+    // coherent load: for memory the same kernel also writes (the read-only path requires data that never changes)
+    static __device__ __forceinline__ Raw load_raw_coherent(const float* p) { return *reinterpret_cast<const Raw*>(p); }
     static __device__ __forceinline__ Raw zero_raw() { return Raw(); }
     static __device__ __forceinline__ void unpack(const Raw& r, float (&f)[V]) {
         if constexpr (V == 4) { f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w); }
@@ -176,6 +178,7 @@ template <int V> struct VecIO<bf16_t, V> {
     static_assert(V == 1 || V == 2 || V == 4 || V == 8, "bf16 vector width");
     typedef typename RawBits<2 * V>::type Raw;
     static __device__ __forceinline__ Raw load_raw(const bf16_t* p) { return ld_stream(reinterpret_cast<const Raw*>(p)); }
+    static __device__ __forceinline__ Raw load_raw_coherent(const bf16_t* p) { return *reinterpret_cast<const Raw*>(p); }
     static __device__ __forceinline__ Raw zero_raw() { return Raw(); }
     static __device__ __forceinline__ void unpack(const Raw& r, float (&f)[V]) {
         if constexpr (V == 8) {

@@ -192,7 +192,8 @@ __global__ void __launch_bounds__(kMaxThreads) write_fwd_kernel(const __grid_con
 // y[m,s,c] = x[m,s,c] + beta[c,s] * dz[m,c]   (rounded to the storage type, as the unfused path stores it)
 // z[m,c]   = sum_s alpha_next[c,s] * y[m,s,c] (read from the ROUNDED carrier, as the unfused path reads it)
 // Moves 2S+2 elements per (token, channel); the unfused pair moves 3S+2.  `y` may be `x` (in place): every
-// element is read and written by the same thread.
+// element is read and written by the same thread, and in that case the carrier is read with ordinary coherent
+// loads (the read-only path is reserved for memory that no thread writes during the kernel).
 template <typename T, typename W, int S, int V, int TT>
 __global__ void __launch_bounds__(kMaxThreads) write_read_kernel(const __grid_constant__ WriteReadParams p) {
     typedef VecIO<T, V> IO;
@@ -202,6 +203,7 @@ __global__ void __launch_bounds__(kMaxThreads) write_read_kernel(const __grid_co
     if (!ln.active) return;
     const T* x = static_cast<const T*>(p.x) + ln.c0;
     T* y = static_cast<T*>(p.y) + ln.c0;
+    const bool in_place = p.x == p.y;            // uniform over the grid
     const T* __restrict__ dz = static_cast<const T*>(p.dz) + ln.c0;
     T* __restrict__ z = static_cast<T*>(p.z) + ln.c0;
     float wb[S][V], wa[S][V];
@@ -227,7 +229,10 @@ __global__ void __launch_bounds__(kMaxThreads) write_read_kernel(const __grid_co
             origin[i] = cell_origin<S>(ok ? m[i] : 0u, t.g, t.C);
             dr[i] = ok ? IO::load_raw(dz + static_cast<size_t>(m[i]) * t.C) : IO::zero_raw();
 #pragma unroll
-            for (int s = 0; s < S; ++s) xr[i][s] = ok ? IO::load_raw(x + origin[i] + slot_offset<S>(s, t.g, t.C)) : IO::zero_raw();
+            for (int s = 0; s < S; ++s) {
+                const T* src = x + origin[i] + slot_offset<S>(s, t.g, t.C);
+                xr[i][s] = !ok ? IO::zero_raw() : (in_place ? IO::load_raw_coherent(src) : IO::load_raw(src));
+            }
         }
         if constexpr (kPacked) {
 #pragma unroll

@@ -33,6 +33,14 @@ def allreduce_weight_grads(grads: Sequence[Tensor], group=None, average: bool = 
         return
     if not grads:
         return
+    world = dist.get_world_size(group)
+    if len(grads) == 1 and grads[0].is_contiguous() and grads[0].dtype == torch.float32:
+        # already one flat fp32 buffer (the kernels can write both gradients into it): reduce it where it lies
+        flat = grads[0].detach()
+        dist.all_reduce(flat, group=group)
+        if average:
+            flat /= world
+        return
     flat = torch.cat([g.detach().reshape(-1).float() for g in grads])
     dist.all_reduce(flat, group=group)
     if average:

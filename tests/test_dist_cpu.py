@@ -32,6 +32,12 @@ def _worker(rank, world, port, tmp, fail):
         allreduce_weight_grads(parts, average=False)
         _, full = O.read_backward(x, g, alpha)
         torch.testing.assert_close(torch.stack(parts), full, atol=1e-5, rtol=1e-5)
+        # one flat fp32 buffer (what the benchmark's kernels write into) is reduced where it lies, as a mean
+        flat = dalpha.clone().float().contiguous()
+        where = flat.data_ptr()
+        allreduce_weight_grads([flat])
+        assert flat.data_ptr() == where
+        torch.testing.assert_close(flat, full / world, atol=1e-5, rtol=1e-5)
         open(os.path.join(tmp, f"ok{rank}"), "w").write("ok")
     except Exception as exc:                                   # noqa: BLE001
         open(os.path.join(tmp, f"err{rank}"), "w").write(repr(exc))

@@ -478,6 +478,39 @@ def test_fused_write_then_read_step_is_the_unfused_pair(R, slots, b, g, c, dtype
     close(z, z2, dtype, "fused vs separate")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("slots,b,g,c", [(4, 4, 16, 768), (4, 3, 7, 67), (16, 2, 4, 64)])
+def test_fused_write_then_read_in_place_through_the_c_abi(slots, b, g, c, dtype):
+    """`y` may be `x` in sihc_write_read_fwd: the carrier is updated where it lies and the result is
+    bit-identical to the out-of-place call (vector and scalar paths)."""
+    from residual_stream_burden_b200 import _lib
+    lib = _lib.lib
+    code = _lib.BF16 if dtype == torch.bfloat16 else _lib.F32
+    torch.manual_seed(77 + slots + c)
+    kh, kw = O.cell_shape(slots)
+    x = torch.randn(b, g * kh, g * kw, c, device=DEV).to(dtype)
+    dz = torch.randn(b, g * g, c, device=DEV).to(dtype)
+    beta = (1.0 + 0.05 * torch.randn(c, slots, device=DEV)).to(dtype)
+    alpha = (1.0 / slots + 0.05 * torch.randn(c, slots, device=DEV)).to(dtype)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call(src, dst, z):
+        rc = lib.sihc_write_read_fwd(src.data_ptr(), dz.data_ptr(), beta.data_ptr(), alpha.data_ptr(), dst.data_ptr(),
+                                     z.data_ptr(), b, g, kh, kw, c, code, code, stream)
+        assert rc == 0, lib.sihc_status_string(rc)
+
+    y_out, z_out = torch.empty_like(x), torch.empty_like(dz)
+    call(x, y_out, z_out)
+    carrier, z_in = x.clone(), torch.empty_like(dz)
+    call(carrier, carrier, z_in)
+    torch.cuda.synchronize()
+    assert torch.equal(carrier, y_out)
+    assert torch.equal(z_in, z_out)
+    oy = O.write(x.cpu(), [dz.cpu()], [beta.cpu()])
+    close(carrier, oy, dtype, "in-place carrier")
+    close(z_in, O.read(oy, alpha.cpu()), dtype, "in-place next read")
+
+
 @pytest.mark.parametrize("slots,c,events", [(4, 4104, 1), (8, 2056, 1), (4, 4104, 3), (2, 4100, 2)])
 def test_channel_counts_wider_than_one_block(R, slots, c, events):
     """More channel vectors than a block has lanes: the channel dimension is tiled over blockIdx.y,

@@ -50,6 +50,11 @@ def test_workspace_queries_and_argument_errors_without_gpu():
     assert lib.sihc_read_fwd(None, None, None, 1, 1, 2, 2, 2, 8, 0, 0, None) == -1
     assert lib.sihc_read_fwd(None, None, None, 1, 1, 2, 2, 2, 8, 0, 1, None) == -2  # bf16 weights with fp32 acts
     assert lib.sihc_tune(b"no_such_knob", 1) == -1
+    # a slot's offset inside its cell row block is kept in 32 bits by the kernels: geometries whose
+    # (kh-1) carrier rows + one cell row reach 2^32 elements are refused, the largest one below is not
+    assert lib.sihc_read_fwd(None, None, None, 1, 1, 128, 4, 4, 1 << 22, 1, 1, None) == -5   # (3*128*4+4)*2^22 >= 2^32
+    assert lib.sihc_read_fwd(None, None, None, 1, 1, 16, 2, 2, 1 << 24, 1, 1, None) == -1   # fits: next check (null)
+    assert lib.sihc_wgrad_workspace_bytes(1, 1, 128, 4, 4, 1 << 22, 1) == 0
 
 
 def test_fake_kernels_trace_on_meta_device():

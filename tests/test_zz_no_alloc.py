@@ -62,13 +62,10 @@ def test_static_scratch_matches_workspace_entry_point_twice(dtype, events, slots
         rc_w, dx_w, da_w = _run(lib, _lib, False, x, gs, alpha, code, code)
         assert rc_s == 0, lib.sihc_status_string(rc_s)
         assert rc_w == 0, lib.sihc_status_string(rc_w)
-        # same tolerances as the parity tests (fp32: rel-L2 1e-5; bf16 storage: 2e-2)
-        for got, want in ((dx_s, dx_w), (da_s, da_w)):
-            got, want = got.float(), want.float()
-            rel = (got - want).norm() / want.norm().clamp_min(1e-12)
-            assert rel <= (1e-5 if dtype == torch.float32 else 2e-2), float(rel)
-            atol, rtol = (2e-4, 2e-4) if dtype == torch.float32 else (0.025, 0.03)
-            torch.testing.assert_close(got, want, atol=atol, rtol=rtol)
+        # Both entry points run the same kernels with the same fixed summation order; only the address of
+        # the partial sums differs.  The results must therefore be identical bit for bit.
+        assert torch.equal(dx_s, dx_w)
+        assert torch.equal(da_s, da_w)
         if events > 1 and call == 1:
             assert torch.count_nonzero(da_s[1]) == 0
 

@@ -433,12 +433,62 @@ def run_stage_ops(args, device, steps, warmup):
     total_ms = sum(v["ms"] for v in res.values())
     total_units = sum(v["units"] for v in res.values())
     value = total_units * tokens * C * esize / total_ms / 1e6
+    comparators = reference_triton_comparator(x, gy, dz, out, w, gam, J, steps, warmup,
+                                              {k: v[1] for k, v in ops.items()}, tokens * C * esize)
     print(json.dumps({"metric": "sihc_stage_ops_bandwidth", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1,
                       "steps": steps, "warmup": warmup, "ms_per_step": round(total_ms, 4), "higher_is_better": True,
                       "dtype": args.dtype, "data": "synthetic",
                       "config": {"workload": f"stage operators, E={E} events, n={S}, width {C}, {tokens} tokens"},
-                      "peak": peak, "peak_source": peak_kind, "ops": res,
+                      "peak": peak, "peak_source": peak_kind, "ops": res, "comparators": comparators,
                       "gpu_launches": int(_lib.launch_count() - launches0)}))
+
+
+def reference_triton_comparator(x, gy, dz, out, w, gam, J, steps, warmup, units, unit_bytes):
+    """The reference's own Triton operators (sihc/models/sihc/sublayer_kernels.py:219-379, unmodified copy under
+    ``oracle/_ref``) timed on the same tensors, same GPU, same method, as a labelled comparator.  Each backward is
+    the call sequence of the reference's autograd formula, run eagerly (its triangular backward leaves the per-edge
+    products to torch, which Inductor would fuse in a compiled model).  Their GB/s use the same byte counts as this library's
+    operators, so the ratio of the two is the ratio of times.  Skipped, with the reason, when the copy is absent,
+    the shape is outside what the reference supports (8/12/16/24 events, 4/16 slots) or Triton cannot compile."""
+    label = "reference Triton operators (sihc/models/sihc/sublayer_kernels.py), same tensors"
+    from oracle.make_ref import ref_path
+    path = ref_path()
+    E, S = w.shape[0], w.shape[2]
+    if path is None:
+        return {"what": label, "skipped": "oracle/_ref is absent"}
+    if E not in (8, 12, 16, 24) or S not in (4, 16):
+        return {"what": label, "skipped": f"the reference has no {E}-event / {S}-slot operator"}
+    try:
+        if path not in sys.path:
+            sys.path.insert(0, path)
+        import sihc.models.sihc.sublayer_kernels as sk
+        g0, gj = out[0], gam[:J].contiguous()
+        calls = {
+            "read_fwd": lambda: sk.sublayer_read(x, w),
+            "triangular_fwd": lambda: sk.sublayer_triangular(g0, dz[:J], gj),
+            "write_fwd": lambda: sk.sublayer_write(x, dz, w),
+            "write_bwd": lambda: (sk.sublayer_read(gy, w), sk._weights_backward(gy, dz, w)),
+            "triangular_bwd": lambda: (sk._tri_gamma_backward(g0, dz[:J], gj),
+                                       [(g0.float() * gj[i].float()).to(g0.dtype) for i in range(J)]),
+            "read_bwd": lambda: (sk._write_impl(x, dz, w, False), sk._weights_backward(x, dz, w)),
+        }
+        res = {}
+        for name, fn in calls.items():
+            for _ in range(max(warmup, 3)):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / steps
+            res[name] = {"ms": round(ms, 4), "GB/s": round(units[name] * unit_bytes / ms / 1e6, 1)}
+        return {"what": label, "triton": __import__("triton").__version__, "ops": res,
+                "ms_total": round(sum(v["ms"] for v in res.values()), 4)}
+    except Exception as exc:                                       # noqa: BLE001
+        return {"what": label, "skipped": repr(exc)[:300]}
 
 
 # ------------------------------------------------------------------------------------------ models
@@ -570,9 +620,24 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
 
 
 # ------------------------------------------------------------------------------------------ CPU
+def cpu_path(slots):
+    """``(read, write, kind)`` of the unfused eager path on the host: the reference's own ``read_torch`` /
+    ``write_torch`` (sihc/bench/fusion_controls.py:14-31) from the unmodified copy under ``oracle/_ref`` when it is
+    there and defines this cell (square cells only), else the oracle's restatement of them."""
+    from oracle.make_ref import ref_path
+    path = ref_path()
+    if path is not None and slots in (4, 16):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+        from sihc.bench import fusion_controls as fc
+        return fc.read_torch, fc.write_torch, "reference"
+    from oracle import sihc_oracle as O
+    return O.read, O.write, "port"
+
+
 def cpu_step_factory(batch, grid, slots, channels, dtype):
     """The reference's unfused eager path on the host: read_torch/write_torch + autograd."""
-    from oracle import sihc_oracle as O
+    read, write, kind = cpu_path(slots)
     inp = make_inputs(batch, grid, slots, channels, dtype, torch.device("cpu"))
 
     def step():
@@ -580,23 +645,24 @@ def cpu_step_factory(batch, grid, slots, channels, dtype):
         alpha = inp["alpha"][0].clone().requires_grad_()
         beta = inp["beta"][0].clone().requires_grad_()
         dz = inp["dz"].clone().requires_grad_()
-        z = O.read(x, alpha)
-        y = O.write(x, [dz], [beta])
+        z = read(x, alpha)
+        y = write(x, [dz], [beta])
         torch.autograd.grad(z, (x, alpha), inp["gz"])
         torch.autograd.grad(y, (dz, beta), inp["gy"])
 
-    return step
+    return step, kind
 
 
 def time_cpu(batch, grid, slots, channels, dtype, reps, warm=1):
+    """Seconds per pass of the host path with every host thread, and which implementation ran."""
     torch.set_num_threads(os.cpu_count() or 1)
-    step = cpu_step_factory(batch, grid, slots, channels, dtype)
+    step, kind = cpu_step_factory(batch, grid, slots, channels, dtype)
     for _ in range(warm):
         step()
     t0 = time.perf_counter()
     for _ in range(reps):
         step()
-    return (time.perf_counter() - t0) / reps
+    return (time.perf_counter() - t0) / reps, kind
 
 
 def main():
@@ -625,14 +691,16 @@ def main():
         sample_tokens = sample_batch * grid * grid
         for _ in range(max(0, min(args.warmup, 1))):
             time_cpu(sample_batch, grid, slots, channels, dtype, 1, warm=0)
-        sec = time_cpu(sample_batch, grid, slots, channels, dtype, max(1, min(args.steps, 10)), warm=0)
+        sec, kind = time_cpu(sample_batch, grid, slots, channels, dtype, max(1, min(args.steps, 10)), warm=0)
         gbs = sum(units.values()) * sample_tokens * channels * esize / sec / 1e9
-        sample = f"{sample_batch} images ({sample_tokens} tokens) of the workload per step, torch eager on CPU"
+        sample = (f"{sample_batch} images ({sample_tokens} tokens) of the workload per step, torch eager on CPU, "
+                  + ("the reference's read_torch / write_torch + autograd" if kind == "reference"
+                     else "the oracle's restatement of read_torch / write_torch + autograd"))
         line = {"impl": "reference", "metric": "sihc_read_write_fwd_bwd_bandwidth", "value": gbs, "unit": "GB/s",
                 "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.dtype,
                 "data": "synthetic", "config": config,
-                "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+                "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
                 "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
         return
@@ -782,10 +850,10 @@ def main():
     cpu = None
     if rank == 0 and not args.no_cpu and world == 1:
         sample_batch = min(batch, 256)                 # about ten seconds of CPU work in total
-        sec = time_cpu(sample_batch, grid, slots, channels, dtype, reps=5)
+        sec, kind = time_cpu(sample_batch, grid, slots, channels, dtype, reps=5)
         sample_tokens = sample_batch * grid * grid
         cpu = {"value": round(sum(units.values()) * sample_tokens * channels * esize / sec / 1e9, 3), "unit": "GB/s",
-               "cores": os.cpu_count() or 1, "kind": "port",
+               "cores": os.cpu_count() or 1, "kind": kind,
                "sample": f"{sample_batch} images ({sample_tokens} tokens) of the workload, torch eager on CPU, "
                          f"{sec * 1e3:.0f} ms per pass"}
 

@@ -58,6 +58,11 @@ def parse_args():
     ap.add_argument("--events", type=int, default=24, help="events per stage for --workload stage_ops")
     ap.add_argument("--no-compile", action="store_true",
                     help="run the models' torch sublayers eagerly instead of under torch.compile")
+    ap.add_argument("--train-impl", default="graph", choices=["graph", "compiled_ddp"],
+                    help="SiHC-XL training step: this package's single-graph step, or whole-model compile + DDP")
+    ap.add_argument("--bucket-mb", type=int, default=256, help="gradient bucket size of the single-graph step")
+    ap.add_argument("--overlap-optimizer", action="store_true",
+                    help="single-graph step: per-bucket AdamW on the side stream right after the bucket's all-reduce")
     ap.add_argument("--sweep", action="store_true",
                     help="bandwidth sweep over n in {2,4,8}, width in {768,1152}, tokens 2^12..2^20: one JSON line per point")
     return ap.parse_args()
@@ -516,7 +521,8 @@ def time_device(fn, steps, warmup, world, device):
     return ms / steps
 
 
-def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_steps=50, compile_model=True):
+def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_steps=50, compile_model=True,
+                   train_impl="graph", bucket_mb=256, overlap_optimizer=False):
     """SiHC-B forward (batch 256), SiHC-XL training step (batch 32 per GPU, DDP) or SiHC-XL Heun sampling
     (batch 256 per GPU, CFG 2.4 on [0.1, 0.9]); bf16 autocast over fp32 parameters, synthetic N(0,1) images,
     random-init weights with opened gates.  Inputs start in pinned host memory every step.
@@ -556,6 +562,32 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
 
         ms = time_device(step, steps, warmup, world, device)
         name = "SiHC-B forward, 12 blocks x 768, n=4, batch 256 per GPU, bf16 autocast, literal fused write+read schedule"
+    elif kind == "sihc_xl_train" and train_impl == "graph":
+        # The whole step - forward, loss, backward, bucketed gradient all-reduce on a side stream, fused AdamW - as
+        # ONE hand-captured CUDA graph; stages run the stage-scoped backward; only the torch sublayers are compiled.
+        from residual_stream_burden_b200.train import TrainStep
+        batch = 32
+        model = sihc_xl().to(device)
+        model.open_gates()
+        trainer = TrainStep(model, batch, lr=2e-4, betas=(0.9, 0.95), weight_decay=0.0, compile_model=compile_model,
+                            bucket_mb=bucket_mb, overlap_optimizer=overlap_optimizer)
+        x_host = torch.randn(batch, 3, 256, 256, generator=gen).pin_memory()
+        y = torch.randint(0, 1000, (batch,), device=device)
+        trainer.step(x_host, y)                     # first eager pass: compiles the sublayers
+        torch.cuda.synchronize()
+        launches0 = _lib.launch_count()
+        trainer.step(x_host, y)                     # second eager pass: counts this library's launches per step
+        torch.cuda.synchronize()
+        per_step_launches = _lib.launch_count() - launches0
+
+        def step():
+            return float(trainer.step(x_host, y))           # H2D copy of the images, graph replay, D2H read of the loss
+
+        ms = time_device(step, steps, warmup, world, device)
+        assert trainer.graph is not None
+        name = ("SiHC-XL training step, 28 blocks x 1152, n=4, stages 8+12+8, batch 32 per GPU, bf16 autocast + fp32 AdamW, "
+                "one CUDA graph per step (stage-scoped backward, gradient all-reduce in %d MB buckets under backward%s)"
+                % (bucket_mb, ", per-bucket AdamW on the side stream" if overlap_optimizer else ""))
     elif kind == "sihc_xl_train":
         batch = 32
         model = sihc_xl().to(device)
@@ -589,7 +621,8 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
             return float(loss.detach())                     # device -> host read of the loss
 
         ms = time_device(step, steps, warmup, world, device)
-        name = "SiHC-XL training step, 28 blocks x 1152, n=4, stages 8+12+8, batch 32 per GPU, bf16 autocast + fp32 AdamW"
+        name = ("SiHC-XL training step, 28 blocks x 1152, n=4, stages 8+12+8, batch 32 per GPU, bf16 autocast + fp32 AdamW, "
+                "whole-model torch.compile + DistributedDataParallel (the reference trainer's arrangement)")
     else:
         batch = 256
         model = sihc_xl().to(device).eval()
@@ -609,7 +642,10 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
 
         ms = time_device(step, steps, warmup, world, device)
         name = f"SiHC-XL Heun sampling, {sample_steps} steps, CFG 2.4 on [0.1,0.9], batch 256 per GPU, bf16 autocast, literal fused write+read schedule"
-    name += ", torch.compile (CUDA graphs) around the torch sublayers" if compile_model else ", eager"
+    if not (kind == "sihc_xl_train" and train_impl == "graph"):
+        name += ", torch.compile (CUDA graphs) around the torch sublayers" if compile_model else ", eager"
+    elif not compile_model:
+        name += ", sublayers not compiled"
     res = {"workload": name, "img_per_s": round(world * batch / (ms * 1e-3), 2),
            "img_per_s_per_gpu": round(batch / (ms * 1e-3), 2), "ms_per_step": round(ms, 3),
            "steps": steps, "warmup": warmup, "global_batch": world * batch, "routing_launches_per_step": per_step_launches,
@@ -731,7 +767,8 @@ def main():
         # one sampling pass is already 2*steps-1 guided evaluations (198 forwards): one warm-up pass is enough there
         warm = max(args.warmup, 1) if args.workload == "sihc_xl_sample" else max(args.warmup, 3)
         res = model_workload(args.workload, device, rank, world, local_rank, args.steps, warm,
-                             args.sample_steps, not args.no_compile)
+                             args.sample_steps, not args.no_compile, args.train_impl, args.bucket_mb,
+                             args.overlap_optimizer)
         clocks = sampler.stop() if rank == 0 else None
         if rank == 0:
             print(json.dumps({"metric": args.workload + "_throughput", "value": res["img_per_s"], "unit": "img/s",
@@ -866,7 +903,8 @@ def main():
         models = {}
         for kind in (("sihc_xl_train", "sihc_b_fwd") if world == 1 else ("sihc_xl_train",)):
             try:
-                models[kind] = model_workload(kind, device, rank, world, local_rank, 20, 8, 50, cm)
+                models[kind] = model_workload(kind, device, rank, world, local_rank, 20, 8, 50, cm,
+                                              args.train_impl, args.bucket_mb, args.overlap_optimizer)
             except Exception as exc:                               # noqa: BLE001
                 if world > 1:
                     raise                                          # see above: never leave the peers waiting

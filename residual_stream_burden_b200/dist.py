@@ -6,7 +6,8 @@ connection event, 2 MB for the largest model here).  Under ``DistributedDataPara
 gradients ride in the ordinary buckets (reference: sihc/training/train.py:515-523).  For
 callers that drive the operators directly, :func:`allreduce_weight_grads` packs any number of
 small gradient tensors into one flat fp32 buffer and issues a single all-reduce, so the exchange
-costs one collective launch regardless of the number of events.
+costs one collective launch regardless of the number of events.  :class:`BucketedGradExchange` averages the
+gradients of a whole model bucket by bucket while the backward pass is still running.
 """
 
 from __future__ import annotations
@@ -50,3 +51,117 @@ def allreduce_weight_grads(grads: Sequence[Tensor], group=None, average: bool = 
         n = g.numel()
         g.detach().copy_(flat[offset:offset + n].view_as(g))
         offset += n
+
+
+class BucketedGradExchange:
+    """Data-parallel gradient averaging that runs UNDER the backward pass instead of after it.
+
+    The parameters are grouped into buckets in the order their gradients become final during backward (the
+    reverse of the order in which the model registered them).  A hook on every parameter counts its bucket down;
+    when a bucket's last gradient has been accumulated its all-reduce is issued at once on a side stream, so it
+    overlaps the backward kernels of the layers below.  :meth:`finish` makes the calling stream wait for all of
+    them.  This is the role ``DistributedDataParallel`` plays in the reference trainer
+    (sihc/training/train.py:515-523) - same arithmetic (mean over ranks, fp32) - built here so that it also works
+    when the backward pass is a sequence of eager autograd nodes captured into one CUDA graph.
+
+    Two ways of presenting a bucket to the collective:
+      * ``in_place=True``: the large gradient tensors are reduced where they lie, all in ONE coalesced call
+        (one collective launch per bucket, no packing copy); only the many small tensors (norm scales, biases,
+        the connection weights) are packed into one flat buffer and copied back;
+      * ``in_place=False``: every gradient of the bucket is packed into one flat buffer (two extra passes over
+        the gradients).
+    With a single rank the hooks still fire (so the bookkeeping is exercised) and the collectives are skipped
+    unless ``force`` is set.
+    """
+
+    def __init__(self, params: Sequence[torch.nn.Parameter], group=None, bucket_bytes: int = 256 << 20,
+                 in_place: bool = True, small_numel: int = 1 << 16, comm_stream=None, force: bool = False,
+                 on_bucket_reduced=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.active = self.world > 1 or (force and dist.is_available() and dist.is_initialized())
+        self.in_place, self.small_numel = in_place, small_numel
+        self.on_bucket_reduced = on_bucket_reduced
+        params = [p for p in params if p.requires_grad]
+        self.buckets: list[list[torch.nn.Parameter]] = []
+        current, size = [], 0
+        for p in reversed(params):                       # backward order
+            current.append(p)
+            size += p.numel() * p.element_size()
+            if size >= bucket_bytes:
+                self.buckets.append(current)
+                current, size = [], 0
+        if current:
+            self.buckets.append(current)
+        self._bucket_of = {id(p): k for k, bucket in enumerate(self.buckets) for p in bucket}
+        self._pending = [0] * len(self.buckets)
+        self._launched = [False] * len(self.buckets)
+        self._handles = []
+        self.cuda = bool(params) and params[0].is_cuda
+        self.comm_stream = comm_stream if comm_stream is not None else (torch.cuda.Stream() if self.cuda else None)
+        backend = dist.get_backend(group) if self.active else None
+        self._avg_op = dist.ReduceOp.AVG if backend == "nccl" else dist.ReduceOp.SUM
+        self._divide = self.active and backend != "nccl"
+        for p in params:
+            self._handles.append(p.register_post_accumulate_grad_hook(self._hook))
+        self.begin()
+
+    # ---- per step ---------------------------------------------------------------------------------------
+    def begin(self) -> None:
+        """Call before every backward pass."""
+        self._pending = [len(b) for b in self.buckets]
+        self._launched = [False] * len(self.buckets)
+
+    def finish(self) -> None:
+        """Call after backward: reduces buckets whose hooks did not all fire (parameters without a gradient this
+        step) and makes the current stream wait for every all-reduce."""
+        for k, done in enumerate(self._launched):
+            if not done:
+                self._reduce(k)
+        if self.cuda:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    def remove(self) -> None:
+        for h in self._handles:
+            h.remove()
+        self._handles = []
+
+    # ---- internals --------------------------------------------------------------------------------------
+    def _hook(self, param) -> None:
+        k = self._bucket_of[id(param)]
+        self._pending[k] -= 1
+        if self._pending[k] == 0 and not self._launched[k]:
+            self._reduce(k)
+
+    def _reduce(self, k: int) -> None:
+        self._launched[k] = True
+        grads = [p.grad for p in self.buckets[k] if p.grad is not None]
+        if self.cuda:
+            # the gradients were produced on the stream this hook runs on: order the side stream after it
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm_stream):
+                self._reduce_on_current_stream(k, grads)
+        else:
+            self._reduce_on_current_stream(k, grads)
+
+    def _reduce_on_current_stream(self, k: int, grads) -> None:
+        if self.active and grads:
+            if self.in_place:
+                large = [g for g in grads if g.numel() >= self.small_numel and g.is_contiguous()]
+                small = [g for g in grads if not (g.numel() >= self.small_numel and g.is_contiguous())]
+            else:
+                large, small = [], list(grads)
+            flat = torch.cat([g.reshape(-1) for g in small]) if small else None
+            tensors = large + ([flat] if flat is not None else [])
+            if len(tensors) == 1:
+                dist.all_reduce(tensors[0], op=self._avg_op, group=self.group)
+            else:
+                with dist._coalescing_manager(group=self.group):        # one collective launch for the bucket
+                    for t in tensors:
+                        dist.all_reduce(t, op=self._avg_op, group=self.group)
+            if self._divide:
+                torch._foreach_div_(tensors, float(self.world))
+            if flat is not None:
+                torch._foreach_copy_(small, [v.view_as(g) for v, g in zip(flat.split([g.numel() for g in small]), small)])
+        if self.on_bucket_reduced is not None:
+            self.on_bucket_reduced(k)

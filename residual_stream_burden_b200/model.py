@@ -29,7 +29,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch import Tensor
 
-from . import ops
+from . import ops, stage
 
 
 def _modulate(x: Tensor, shift: Tensor, scale: Tensor) -> Tensor:
@@ -279,6 +279,10 @@ class SiHC(nn.Module):
         # "literal": write event i and read event i+1 in one pass over the carrier, no triangular step;
         # forward-only, fewer bytes than the factored stage when n <= 4 (10 vs ~16 elements per event at E=24).
         self.inference_schedule = "factored"
+        # "per_op": every routing operator carries its own autograd formula (traceable by torch.compile).
+        # "stage": the stage-scoped backward of :mod:`.stage` - lazily transposed triangular accumulation, one
+        # gamma-gradient pass per stage; eager only (a Python tape), can be captured in a CUDA graph.
+        self.training_schedule = "per_op"
         self.reset_parameters()
 
     def reset_parameters(self) -> None:
@@ -358,6 +362,17 @@ class SiHC(nn.Module):
         events = self.stage_events(blocks, cond, stage_start)
         alpha = torch.stack([c.alpha(dtype=x0.dtype) for c, _, _ in events]).contiguous()
         beta = torch.stack([c.beta(dtype=x0.dtype) for c, _, _ in events]).contiguous()
+        if self.training_schedule == "stage":
+            state = [context]
+
+            def sublayer(update, uses_context):
+                def run(z):
+                    dz, state[0] = self.apply_update(update, z, state[0], uses_context)
+                    return dz
+                return run
+
+            out = stage.run_stage(x0, alpha, beta, [sublayer(u, c) for _, u, c in events])
+            return out, state[0]
         base = ops.sublayer_read(x0, alpha)
         gamma = (alpha[:, None] * beta[None, :]).sum(dim=-1)
         updates: list[Tensor] = []

@@ -75,3 +75,58 @@ def test_shard_batch_partitions_exactly():
             assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
     with pytest.raises(ValueError):
         shard_batch(8, 2, 2)
+
+
+def _bucket_worker(rank, world, port, tmp, in_place):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+    from residual_stream_burden_b200.dist import BucketedGradExchange, shard_batch
+    try:
+        torch.manual_seed(0)                                   # same model and full batch on every rank
+        net = torch.nn.Sequential(torch.nn.Linear(12, 40), torch.nn.Tanh(), torch.nn.Linear(40, 40), torch.nn.Tanh(),
+                                  torch.nn.Linear(40, 3))
+        unused = torch.nn.Parameter(torch.ones(5))             # a parameter that never gets a gradient
+        x, y = torch.randn(8, 12), torch.randn(8, 3)
+        order = []
+        params = list(net.parameters()) + [unused]
+        ex = BucketedGradExchange(params, bucket_bytes=500, in_place=in_place, small_numel=100,
+                                  on_bucket_reduced=order.append)
+        assert len(ex.buckets) >= 3
+        assert ex.buckets[0][0] is unused and ex.buckets[0][1] is net[4].bias          # backward order
+        for _ in range(2):                                     # two steps: the bookkeeping resets
+            for p in params:
+                p.grad = None
+            order.clear()
+            lo, hi = shard_batch(8, rank, world)
+            ex.begin()
+            (net(x[lo:hi]) - y[lo:hi]).square().mean().backward()
+            launched_by_hooks = list(order)
+            ex.finish()
+            assert sorted(order) == list(range(len(ex.buckets)))
+            assert launched_by_hooks == sorted(launched_by_hooks) and len(launched_by_hooks) >= len(ex.buckets) - 1
+            got = [p.grad.clone() for p in net.parameters()]
+            for p in net.parameters():
+                p.grad = None
+            (net(x) - y).square().mean().backward()            # full batch on one process = mean over the two shards
+            for a, p in zip(got, net.parameters()):
+                torch.testing.assert_close(a, p.grad, atol=1e-6, rtol=1e-5)
+            assert unused.grad is None
+        ex.remove()
+        open(os.path.join(tmp, f"ok{rank}"), "w").write("ok")
+    except Exception as exc:                                   # noqa: BLE001
+        import traceback
+        open(os.path.join(tmp, f"err{rank}"), "w").write(traceback.format_exc())
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:                                      # noqa: BLE001
+            pass
+
+
+@pytest.mark.parametrize("in_place", [True, False])
+def test_bucketed_exchange_averages_gradients_during_backward(tmp_path, in_place):
+    mp.spawn(_bucket_worker, args=(2, _port(), str(tmp_path), in_place), nprocs=2, join=True)
+    errs = [p.read_text() for p in tmp_path.iterdir() if p.name.startswith("err")]
+    assert not errs, errs[0]
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()

@@ -38,6 +38,24 @@ if ROOT not in sys.path:
 CELLS = {2: (1, 2), 4: (2, 2), 8: (2, 4), 16: (4, 4)}
 
 
+def shutdown_group():
+    """Leave the process group.  The result line is already printed when this runs; should the teardown of the
+    collective library ever block (it waits for every captured graph that holds its collectives to be destroyed),
+    a timer ends this process after a minute instead of leaving the job's GPUs occupied."""
+    import gc
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()):
+        return
+    sys.stdout.flush()
+    timer = threading.Timer(60.0, os._exit, args=(0,))
+    timer.daemon = True
+    timer.start()
+    gc.collect()
+    torch.cuda.synchronize()
+    dist.destroy_process_group()
+    timer.cancel()
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -404,7 +422,9 @@ def run_stage_ops(args, device, steps, warmup):
     gam = rnd(E, C, std=0.05)
     dw = torch.empty(E, C, S, device=device, dtype=torch.float32)
     dgam = torch.empty(E, C, device=device, dtype=torch.float32)
-    nbytes = max(lib.sihc_wgrad_workspace_bytes(E, B, g, kh, kw, C, code), lib.sihc_tri_workspace_bytes(E, tokens, C, code), 16)
+    nbytes = max(lib.sihc_wgrad_workspace_bytes(E, B, g, kh, kw, C, code), lib.sihc_tri_workspace_bytes(E, tokens, C, code),
+                 lib.sihc_tri_dgamma_workspace_bytes(E, tokens, C, code), 16)
+    dgam_full = torch.empty(E, E, C, device=device, dtype=torch.float32)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
     st = torch.cuda.current_stream().cuda_stream
     pa = _lib.ptr_array
@@ -419,6 +439,8 @@ def run_stage_ops(args, device, steps, warmup):
         "triangular_bwd": (lambda: lib.sihc_tri_bwd(out[0].data_ptr(), p_dz, gam.data_ptr(), p_out, dgam.data_ptr(), ws.data_ptr(), ws.numel(), J, tokens, C, code, code, st), 2 * J + 1),
         "read_bwd": (lambda: lib.sihc_read_bwd(x.data_ptr(), p_dz, w.data_ptr(), y.data_ptr(), dw.data_ptr(), ws.data_ptr(), ws.numel(), E, *geom), 2 * (S + E)),
     }
+    if E > 1:       # whole-stage coefficient gradient of the stage-scoped backward: every tensor read once
+        ops["stage_dgamma"] = (lambda: lib.sihc_tri_dgamma(p_out, p_dz, dgam_full.data_ptr(), ws.data_ptr(), ws.numel(), E, tokens, C, code, st), 2 * (E - 1))
     peak, peak_kind = load_peaks()
     res = {}
     launches0 = _lib.launch_count()
@@ -439,7 +461,7 @@ def run_stage_ops(args, device, steps, warmup):
     total_units = sum(v["units"] for v in res.values())
     value = total_units * tokens * C * esize / total_ms / 1e6
     comparators = reference_triton_comparator(x, gy, dz, out, w, gam, J, steps, warmup,
-                                              {k: v[1] for k, v in ops.items()}, tokens * C * esize)
+                                              {k: v[1] for k, v in ops.items() if k != "stage_dgamma"}, tokens * C * esize)
     print(json.dumps({"metric": "sihc_stage_ops_bandwidth", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1,
                       "steps": steps, "warmup": warmup, "ms_per_step": round(total_ms, 4), "higher_is_better": True,
                       "dtype": args.dtype, "data": "synthetic",
@@ -583,8 +605,11 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         def step():
             return float(trainer.step(x_host, y))           # H2D copy of the images, graph replay, D2H read of the loss
 
-        ms = time_device(step, steps, warmup, world, device)
-        assert trainer.graph is not None
+        try:
+            ms = time_device(step, steps, warmup, world, device)
+            assert trainer.graph is not None
+        finally:
+            trainer.close()        # the graph holds captured collectives: it must be gone before the group is destroyed
         name = ("SiHC-XL training step, 28 blocks x 1152, n=4, stages 8+12+8, batch 32 per GPU, bf16 autocast + fp32 AdamW, "
                 "one CUDA graph per step (stage-scoped backward, gradient all-reduce in %d MB buckets under backward%s)"
                 % (bucket_mb, ", per-bucket AdamW on the side stream" if overlap_optimizer else ""))
@@ -752,13 +777,13 @@ def main():
     if args.sweep:
         run_sweep(args, device, rank, world)
         if world > 1:
-            dist.destroy_process_group()
+            shutdown_group()
         return
     if args.workload == "stage_ops":
         if rank == 0:
             run_stage_ops(args, device, args.steps, max(args.warmup, 3))
         if world > 1:
-            dist.destroy_process_group()
+            shutdown_group()
         return
     if args.workload != "op":
         sampler = ClockSampler(local_rank)
@@ -780,7 +805,7 @@ def main():
                               "gpu_launches": res["routing_launches_per_step"] * args.steps,
                               "peak_mem_gb": res["peak_mem_gb"], "clocks": clocks}))
         if world > 1:
-            dist.destroy_process_group()
+            shutdown_group()
         return
 
     from residual_stream_burden_b200.dist import allreduce_weight_grads
@@ -920,7 +945,7 @@ def main():
                 "clocks": clocks, "models": models}
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        shutdown_group()
 
 
 if __name__ == "__main__":

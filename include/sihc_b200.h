@@ -190,6 +190,21 @@ int sihc_tri_bwd(const void* grad, const void* const* dz, const void* gamma, voi
                  float* dgamma, void* workspace, size_t workspace_bytes, int active,
                  int64_t tokens, int channels, int dtype, int gdtype, void* stream);
 
+/* Scratch bytes for sihc_tri_dgamma. */
+size_t sihc_tri_dgamma_workspace_bytes(int events, int64_t tokens, int channels, int dtype);
+
+/*
+ * Gradient of a whole stage's triangular coefficients in one pass.
+ *   dgamma[i,j,c] = sum_m g[i][m,c] * dz[j][m,c]   for j < i < events;  0 elsewhere   (fp32, [events,events,channels])
+ * g[i] is the gradient that reached event i's accumulated read (g[0] is not read; a NULL g[i] is a read that was
+ * never used and gives a zero row), dz[j] is event j's update (dz[events-1] is not read).  Every tensor is read once:
+ * 2(events-1) workspace tensors instead of the events^2/2 of one `_tri_gamma_backward` + `_triangular_gamma_grad`
+ * call per event (sihc/models/sihc/sublayer_kernels.py:355-361, :324-334), which this replaces for a stage whose
+ * backward is scheduled as a whole.  Deterministic (per-block partial sums in `workspace`, fixed-order finish).
+ */
+int sihc_tri_dgamma(const void* const* g, const void* const* dz, float* dgamma, void* workspace,
+                    size_t workspace_bytes, int events, int64_t tokens, int channels, int dtype, void* stream);
+
 /*
  * Benchmark-only knob: override a launch parameter by name; never needed for
  * correct results.  Process-global and not thread-safe.  "partial_blocks_per_sm" and

@@ -33,6 +33,9 @@ SIGNATURES = {
     "sihc_tri_workspace_bytes": (c_size_t, [c_int, c_int64, c_int, c_int]),
     "sihc_tri_bwd": (c_int, [c_void_p, POINTER(c_void_p), c_void_p, POINTER(c_void_p), c_void_p, c_void_p, c_size_t,
                              c_int, c_int64, c_int, c_int, c_int, c_void_p]),
+    "sihc_tri_dgamma_workspace_bytes": (c_size_t, [c_int, c_int64, c_int, c_int]),
+    "sihc_tri_dgamma": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_void_p, c_void_p, c_size_t, c_int, c_int64, c_int,
+                                c_int, c_void_p]),
     "sihc_tune": (c_int, [c_char_p, c_int]),
     "sihc_launch_count": (c_uint64, []),
 }

@@ -176,7 +176,7 @@ using namespace sihc;
 
 extern "C" {
 
-int sihc_version(void) { return 1; }
+int sihc_version(void) { return 2; }
 
 const char* sihc_status_string(int status) {
     switch (status) {
@@ -414,6 +414,49 @@ int sihc_tri_bwd(const void* grad, const void* const* dz, const void* gamma, voi
     cudaError_t e = launch_tri_bwd(pb, grad, dz ? dz : no_dz, gamma, want_ddz ? ddz : nullptr, partial, &blocks);
     if (e == cudaSuccess && dgamma)
         e = launch_finish(partial, dgamma, blocks, static_cast<uint32_t>(active), pb.C, 1, pb.stream);
+    return status_of(e);
+}
+
+size_t sihc_tri_dgamma_workspace_bytes(int events, int64_t tokens, int channels, int dtype) {
+    Problem pb;
+    if (make_tri_problem(pb, events, tokens, channels, dtype, dtype, nullptr)) return 0;
+    if (events < 2) return 0;
+    // the larger of the one-pass kernel's scratch and the per-event form's (used when vector access is not possible)
+    const size_t one_pass = tri_dgamma_workspace_bytes(events, pb.M, pb.C, esize(dtype));
+    const size_t per_event = sihc_tri_workspace_bytes(events - 1, tokens, channels, dtype);
+    return one_pass > per_event ? one_pass : per_event;
+}
+
+int sihc_tri_dgamma(const void* const* g, const void* const* dz, float* dgamma, void* workspace, size_t workspace_bytes,
+                    int events, int64_t tokens, int channels, int dtype, void* stream) {
+    Problem pb;
+    if (int st = make_tri_problem(pb, events, tokens, channels, dtype, dtype, stream)) return st;
+    if (!g || !dz || !dgamma) return SIHC_ERR_NULL;
+    if (!aligned(dgamma, 4)) return SIHC_ERR_ALIGN;
+    bool vec = (static_cast<size_t>(pb.C) * esize(dtype)) % 16 == 0;
+    for (int l = 0; l < events; ++l) {
+        if (l + 1 < events) { if (!dz[l]) return SIHC_ERR_NULL; if (!aligned(dz[l], esize(dtype))) return SIHC_ERR_ALIGN; vec = vec && aligned(dz[l], 16); }
+        if (l > 0 && g[l]) { if (!aligned(g[l], esize(dtype))) return SIHC_ERR_ALIGN; vec = vec && aligned(g[l], 16); }
+    }
+    if (tuning().maxvec_bytes > 0 && tuning().maxvec_bytes < 16) vec = false;
+    if (events >= 2)
+        if (int st = check_workspace(workspace, workspace_bytes, sihc_tri_dgamma_workspace_bytes(events, tokens, channels, dtype))) return st;
+    float* partial = static_cast<float*>(workspace);
+    if (vec) {
+        pb.V = 4;
+        return status_of(launch_tri_dgamma(pb, g, dz, partial, dgamma));
+    }
+    // scalar path: one per-event reduction per row of the matrix, rows of unused reads and the upper triangle stay zero
+    cudaError_t e = cudaMemsetAsync(dgamma, 0, static_cast<size_t>(events) * events * pb.C * sizeof(float), pb.stream);
+    for (int i = 1; i < events && e == cudaSuccess; ++i) {
+        if (!g[i]) continue;
+        Problem row = pb;
+        row.E = i; row.V = 1;
+        uint32_t blocks = 0;
+        e = launch_tri_bwd(row, g[i], dz, dz[0], nullptr, partial, &blocks);     // no ddz: the coefficients are not read
+        if (e == cudaSuccess)
+            e = launch_finish(partial, dgamma + static_cast<size_t>(i) * events * pb.C, blocks, static_cast<uint32_t>(i), pb.C, 1, pb.stream);
+    }
     return status_of(e);
 }
 

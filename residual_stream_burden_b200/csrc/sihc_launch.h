@@ -87,6 +87,13 @@ cudaError_t launch_tri_fwd(const Problem& pb, const void* base, const void* cons
 cudaError_t launch_tri_bwd(const Problem& pb, const void* grad, const void* const* dz, const void* gamma,
                            void* const* ddz, float* partial, uint32_t* blocks);
 
+// Whole-stage coefficient gradient dgamma[i][j][c] = sum_m g_i * dz_j (j < i; zero elsewhere), [E][E][C] fp32, from one
+// pass over the E-1 recorded gradients and E-1 updates (sihc_trigamma.cu).  Needs C * element size % 16 == 0 and
+// 16-byte aligned tensors.  g[0] and dz[E-1] are not read; a null g[i] gives a zero row.
+size_t tri_dgamma_workspace_bytes(int E, uint32_t M, uint32_t C, size_t esize);
+cudaError_t launch_tri_dgamma(const Problem& pb, const void* const* g, const void* const* dz, float* partial,
+                              float* dgamma);
+
 // ---- shared launch plumbing -------------------------------------------------------------------
 struct BlockShape { uint32_t cl, tl, gy, threads; };
 

@@ -283,6 +283,7 @@ class SiHC(nn.Module):
         # "stage": the stage-scoped backward of :mod:`.stage` - lazily transposed triangular accumulation, one
         # gamma-gradient pass per stage; eager only (a Python tape), can be captured in a CUDA graph.
         self.training_schedule = "per_op"
+        self.coefficients = SiHC.stage_coefficients
         self.reset_parameters()
 
     def reset_parameters(self) -> None:
@@ -329,6 +330,16 @@ class SiHC(nn.Module):
         return x.reshape(b, h, h, p, p, c).permute(0, 5, 1, 3, 2, 4).reshape(b, c, h * p, h * p)
 
     # ---- the hot path's caller -----------------------------------------------------------------
+    @staticmethod
+    def stage_coefficients(read_weights: Sequence[Tensor], write_weights: Sequence[Tensor], dtype: torch.dtype):
+        """``alpha, beta [E,C,S]`` in the carrier dtype and ``gamma[i,j,c] = sum_s alpha_i[c,s] beta_j[c,s]`` from the
+        stage's fp32 parameters (reference: sihc/models/sihc/sublayer.py:57-60).  A few dozen tiny torch kernels
+        with their autograd; a training step may swap in a compiled version through ``self.coefficients``."""
+        alpha = torch.stack([w.to(dtype=dtype) for w in read_weights]).contiguous()
+        beta = torch.stack([w.to(dtype=dtype) for w in write_weights]).contiguous()
+        gamma = (alpha[:, None] * beta[None, :]).sum(dim=-1)
+        return alpha, beta, gamma
+
     def stage_events(self, blocks: Sequence[nn.Module], cond: Tensor, stage_start: int) -> list:
         """The connection events of a stage, in order: ``(connection, update, uses_context)`` where
         ``update(seq, rope)`` is the gated sublayer (or whole-block) update of a token sequence."""
@@ -360,8 +371,8 @@ class SiHC(nn.Module):
         """One fused stage (reference: ``_run_fused_schedule_stage``, sihc/models/sihc/sublayer.py:52-72, :84-122;
         block-wise sihc/models/sihc/model.py:430-473, :588-639).  Returns ``(carrier, context)``."""
         events = self.stage_events(blocks, cond, stage_start)
-        alpha = torch.stack([c.alpha(dtype=x0.dtype) for c, _, _ in events]).contiguous()
-        beta = torch.stack([c.beta(dtype=x0.dtype) for c, _, _ in events]).contiguous()
+        alpha, beta, gamma = self.coefficients(tuple(c.read_weight for c, _, _ in events),
+                                               tuple(c.write_weight for c, _, _ in events), x0.dtype)
         if self.training_schedule == "stage":
             state = [context]
 
@@ -371,10 +382,9 @@ class SiHC(nn.Module):
                     return dz
                 return run
 
-            out = stage.run_stage(x0, alpha, beta, [sublayer(u, c) for _, u, c in events])
+            out = stage.run_stage(x0, alpha, beta, [sublayer(u, c) for _, u, c in events], gamma=gamma)
             return out, state[0]
         base = ops.sublayer_read(x0, alpha)
-        gamma = (alpha[:, None] * beta[None, :]).sum(dim=-1)
         updates: list[Tensor] = []
         for e, (_, update, uses_context) in enumerate(events):
             z = base[e] if e == 0 else ops.sublayer_triangular(base[e], updates, gamma[e, :e].contiguous())

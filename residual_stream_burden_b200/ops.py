@@ -333,6 +333,41 @@ def _tri_backward(ctx, grad):
 register_autograd(sublayer_triangular, _tri_backward, setup_context=_tri_setup)
 
 
+@custom_op("sihc_b200::stage_gamma_backward", mutates_args=())
+def _stage_gamma_backward_op(grads: List[Optional[Tensor]], updates: List[Tensor], gamma: Tensor) -> Tensor:
+    """``dgamma[i,j,c] = sum_m grads[i] * updates[j]`` for ``j < i`` (zero elsewhere), the gradient of a whole
+    stage's coefficient matrix ``gamma [E,E,C]`` in one pass over the recorded gradients and the updates.
+
+    ``grads[i]`` is the gradient that reached event i's accumulated read (``grads[0]`` is ignored; ``None`` = the
+    read was never used: zero row).  Replaces one ``_tri_gamma_backward`` call per event
+    (sihc/models/sihc/sublayer_kernels.py:355-361).  Returned in ``gamma.dtype`` (fp32 accumulation).
+    """
+    e = gamma.shape[0]
+    if gamma.ndim != 3 or gamma.shape[1] != e or len(grads) != e or len(updates) != e:
+        raise ValueError("expected gamma [events, events, channels] and one gradient slot and one update per event")
+    ref = updates[0]
+    _require_packed("stage gamma backward", gamma=gamma)
+    for t in list(updates) + [g for g in grads if g is not None]:
+        _require_packed("stage gamma backward", tensor=t)
+        if t.shape != ref.shape or t.dtype != ref.dtype or t.device != ref.device:
+            raise ValueError("gradients and updates must share shape, dtype and device")
+    if ref.ndim != 3 or ref.shape[-1] != gamma.shape[-1] or ref.dtype not in _DTYPES or not ref.is_cuda:
+        raise ValueError("expected CUDA workspace tensors [batch, tokens, channels] matching gamma's channels")
+    b, n, c = ref.shape
+    dgamma = torch.empty((e, e, c), device=ref.device, dtype=torch.float32)
+    with torch.cuda.device(ref.device):
+        nbytes = lib.sihc_tri_dgamma_workspace_bytes(e, b * n, c, _DTYPES[ref.dtype])
+        ws = _workspace(nbytes, ref.device)
+        check(lib.sihc_tri_dgamma(_ptrs(grads), _ptrs(updates), dgamma.data_ptr(), ws.data_ptr(), ws.numel(), e, b * n, c,
+                                  _DTYPES[ref.dtype], _stream(ref)), "sihc_tri_dgamma")
+    return dgamma.to(gamma.dtype)
+
+
+@_stage_gamma_backward_op.register_fake
+def _stage_gamma_backward_fake(grads, updates, gamma):
+    return torch.empty_like(gamma)
+
+
 # --------------------------------------------------------------------------- single-event API
 class _SihcRead(torch.autograd.Function):
     """Single-event read as a plain autograd Function (eager path)."""

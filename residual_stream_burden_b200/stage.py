@@ -74,15 +74,10 @@ class _GammaGate(torch.autograd.Function):
         tape: StageTape = ctx.tape
         if not ctx.needs_input_grad[0]:
             return None, None
-        gamma = tape.gamma
-        dgamma = torch.zeros_like(gamma)
-        for i in range(1, tape.events):
-            g = tape.grads[i]
-            if g is None:               # event i's read was never used downstream
-                continue
-            _, row = ops._tri_backward_op(g, tape.updates[:i], gamma[i, :i].contiguous(), False, True)
-            dgamma[i, :i] = row
-        return dgamma, None
+        if tape.events < 2 or all(g is None for g in tape.grads[1:]):
+            return torch.zeros_like(tape.gamma), None
+        # every recorded gradient and every update is read once; rows of unused reads come out zero
+        return ops._stage_gamma_backward_op(tape.grads, tape.updates, tape.gamma), None
 
 
 class _Accumulate(torch.autograd.Function):
@@ -129,19 +124,22 @@ class _Inject(torch.autograd.Function):
         return None, None, ops.sublayer_triangular(base, g_list, coeff)
 
 
-def run_stage(x0: Tensor, alpha: Tensor, beta: Tensor, sublayers: Sequence[Callable[[Tensor], Tensor]]) -> Tensor:
+def run_stage(x0: Tensor, alpha: Tensor, beta: Tensor, sublayers: Sequence[Callable[[Tensor], Tensor]],
+              gamma: Optional[Tensor] = None) -> Tensor:
     """One fused stage with the stage-scoped backward.
 
     ``alpha`` / ``beta`` are ``[E, C, S]`` in the carrier dtype (or fp32); ``sublayers[i](z_i)`` returns event i's
     update ``dz_i`` (any torch code; the result is made contiguous).  Same values as the per-operator stage of
     :meth:`residual_stream_burden_b200.model.SiHC.run_stage`; gradients agree to rounding (sums are formed in
-    fp32 inside one kernel here, pair by pair in the storage dtype there).
+    fp32 inside one kernel here, pair by pair in the storage dtype there).  ``gamma`` may be passed when the caller
+    has already formed ``sum_s alpha_i * beta_j`` (``[E, E, C]``, differentiable).
     """
     events = alpha.shape[0]
     if len(sublayers) != events or beta.shape != alpha.shape:
         raise ValueError("one sublayer per connection event and matching read/write weights are required")
     base = ops.sublayer_read(x0, alpha)
-    gamma = (alpha[:, None] * beta[None, :]).sum(dim=-1)
+    if gamma is None:
+        gamma = (alpha[:, None] * beta[None, :]).sum(dim=-1)
     tape = StageTape(events)
     gamma = _GammaGate.apply(gamma, tape)
     updates: List[Tensor] = []

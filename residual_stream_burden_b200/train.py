@@ -56,6 +56,9 @@ def compile_sublayers(model: SiHC) -> SiHC:
         branch.mlp_update = functools.partial(mlp, branch)
         branch.forward = functools.partial(whole, branch)
     model.final_layer.forward = torch.compile(model.final_layer.forward, fullgraph=True, dynamic=False)
+    # casts, stacking and the gamma products of a stage's connection weights: one small compiled graph per stage
+    # size instead of a few dozen tiny kernels (and as many again in backward)
+    model.coefficients = torch.compile(SiHC.stage_coefficients, fullgraph=True, dynamic=False)
     return model
 
 
@@ -69,7 +72,7 @@ class TrainStep:
     """
 
     def __init__(self, model: SiHC, batch: int, *, lr: float = 2e-4, betas=(0.9, 0.95), weight_decay: float = 0.0,
-                 group=None, bucket_mb: int = 256, in_place_exchange: bool = True, overlap_optimizer: bool = False,
+                 group=None, bucket_mb: float = 256, in_place_exchange: bool = True, overlap_optimizer: bool = False,
                  compile_model: bool = True, use_graph: bool = True, force_exchange: bool = False, warmup: int = 3):
         device = next(model.parameters()).device
         if device.type != "cuda":
@@ -89,7 +92,7 @@ class TrainStep:
         opt_kw = dict(lr=lr, betas=betas, weight_decay=weight_decay, fused=True, capturable=use_graph)
         self.bucket_optimizers = None
         if distributed or overlap_optimizer:
-            self.exchange = BucketedGradExchange(params, group=group, bucket_bytes=bucket_mb << 20,
+            self.exchange = BucketedGradExchange(params, group=group, bucket_bytes=int(bucket_mb * (1 << 20)),
                                                  in_place=in_place_exchange, force=force_exchange,
                                                  on_bucket_reduced=self._bucket_ready if overlap_optimizer else None)
         if overlap_optimizer:
@@ -154,3 +157,26 @@ class TrainStep:
     def step(self, images_host: Tensor, labels: Tensor) -> Tensor:
         self.load(images_host, labels)
         return self.run()
+
+    def close(self) -> None:
+        """Destroy the captured graph and detach the gradient hooks.
+
+        Call this before the process group is destroyed: a communicator whose collectives were captured waits, when
+        it is torn down, until every graph that holds them is gone, so a graph kept alive past
+        ``destroy_process_group()`` (for instance by a reference cycle) blocks the exit of the process.
+        """
+        torch.cuda.synchronize(self.device)
+        if self.graph is not None:
+            self.graph.reset()
+            self.graph = None
+        if self.exchange is not None:
+            self.exchange.remove()
+            self.exchange.on_bucket_reduced = None       # breaks the trainer <-> exchange reference cycle
+        self._warmup_left = 1 << 30                      # any later step runs eagerly
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+        return False

@@ -606,3 +606,46 @@ def test_pointers_off_the_16_byte_grid_take_the_scalar_path(R, dtype, events):
     gamma = _misaligned((torch.randn(events, c) * 0.05).to(dtype))
     out = R.sublayer_triangular(base, dzd, gamma)
     close(out, O.triangular(base.cpu(), dz, gamma.cpu()), dtype, "triangular")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("events,tokens,c", [(24, 1030, 768), (16, 515, 1152), (12, 300, 72), (8, 257, 64), (5, 99, 40),
+                                             (2, 33, 16), (24, 70, 37), (7, 50, 36), (1, 10, 16)])
+def test_stage_coefficient_gradient_in_one_pass(events, tokens, c, dtype):
+    """sihc_tri_dgamma: dgamma[i,j,c] = sum_m g_i * dz_j for j < i, zero elsewhere, against an fp64 sum; vector
+    path, channel tails, the scalar path (37 and, in bf16, 36 channels), an unused read (NULL gradient) and the
+    one-event stage.  Deterministic: two calls give identical bits."""
+    from residual_stream_burden_b200 import _lib
+    lib = _lib.lib
+    code = _lib.BF16 if dtype == torch.bfloat16 else _lib.F32
+    torch.manual_seed(events * 1000 + c)
+    g = [torch.randn(1, tokens, c, device=DEV).to(dtype) for _ in range(events)]
+    dz = [torch.randn(1, tokens, c, device=DEV).to(dtype) for _ in range(events)]
+    unused = 2 if events > 3 else None
+    ptr_g = _lib.ptr_array([None if i == unused else t.data_ptr() for i, t in enumerate(g)])
+    ptr_dz = _lib.ptr_array([t.data_ptr() for t in dz])
+    nbytes = lib.sihc_tri_dgamma_workspace_bytes(events, tokens, c, code)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    outs = []
+    for _ in range(2):
+        out = torch.full((events, events, c), float("nan"), device=DEV)
+        rc = lib.sihc_tri_dgamma(ptr_g, ptr_dz, out.data_ptr(), ws.data_ptr(), ws.numel(), events, tokens, c, code, stream)
+        assert rc == 0, lib.sihc_status_string(rc)
+        outs.append(out)
+        ws.fill_(0xFF)                                   # the scratch needs no particular contents
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
+    G = torch.stack([t[0].double() for t in g])          # [E, M, C]
+    D = torch.stack([t[0].double() for t in dz])
+    want = torch.einsum("imc,jmc->ijc", G, D)
+    mask = torch.tril(torch.ones(events, events, device=DEV), diagonal=-1)
+    if unused is not None:
+        mask[unused] = 0
+    want = want * mask[:, :, None]
+    got = outs[0].double()
+    assert torch.count_nonzero(got * (1 - mask[:, :, None])) == 0          # exactly zero outside the lower triangle
+    if events > 1:
+        rel = (got - want).norm() / want.norm()
+        assert rel <= 1e-5, float(rel)                     # fp32 accumulation of exact products
+        torch.testing.assert_close(got, want, atol=2e-4 * tokens ** 0.5, rtol=2e-4)

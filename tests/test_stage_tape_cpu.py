@@ -19,15 +19,18 @@ from oracle import sihc_oracle as O
 
 def oracle_ops():
     """Differentiable CPU stand-ins with the signatures :mod:`stage` calls."""
-    def tri_backward_op(grad, updates, gamma, need_ddz, need_dgamma):
-        ddz, dgamma = O.triangular_backward(grad, updates, gamma)
-        return (ddz if need_ddz else []), dgamma.to(gamma.dtype)
+    def stage_gamma_backward_op(grads, updates, gamma):
+        dgamma = torch.zeros_like(gamma)
+        for i in range(1, gamma.shape[0]):
+            if grads[i] is not None:
+                dgamma[i, :i] = O.triangular_backward(grads[i], updates[:i], gamma[i, :i])[1].to(gamma.dtype)
+        return dgamma
 
     return types.SimpleNamespace(
         sublayer_read=lambda x, alpha: O.multi_read(x, alpha),
         sublayer_write=lambda x, updates, beta: O.write(x, updates, beta),
         sublayer_triangular=lambda base, updates, gamma: O.triangular(base, updates, gamma),
-        _tri_backward_op=tri_backward_op,
+        _stage_gamma_backward_op=stage_gamma_backward_op,
     )
 
 

@@ -79,8 +79,12 @@ def parse_args():
     ap.add_argument("--train-impl", default="graph", choices=["graph", "compiled_ddp"],
                     help="SiHC-XL training step: this package's single-graph step, or whole-model compile + DDP")
     ap.add_argument("--bucket-mb", type=int, default=256, help="gradient bucket size of the single-graph step")
-    ap.add_argument("--overlap-optimizer", action="store_true",
-                    help="single-graph step: per-bucket AdamW on the side stream right after the bucket's all-reduce")
+    ap.add_argument("--no-overlap-optimizer", dest="overlap_optimizer", action="store_false",
+                    help="single-graph step: one AdamW update after backward instead of per-bucket updates on the side "
+                         "stream right after each bucket's all-reduce")
+    ap.add_argument("--sweep-slots", default="2,4,8", help="n values of --sweep")
+    ap.add_argument("--sweep-channels", default="768,1152", help="widths of --sweep")
+    ap.add_argument("--sweep-log2", default="12-20", help="range lo-hi of log2(tokens) of --sweep")
     ap.add_argument("--sweep", action="store_true",
                     help="bandwidth sweep over n in {2,4,8}, width in {768,1152}, tokens 2^12..2^20: one JSON line per point")
     return ap.parse_args()
@@ -342,9 +346,10 @@ def run_sweep(args, device, rank, world):
     esize = 2 if dtype == torch.bfloat16 else 4
     peak, peak_kind = load_peaks()
     grid = 16
-    for slots in (2, 4, 8):
-        for channels in (768, 1152):
-            for log2m in range(12, 21):
+    lo, hi = (int(v) for v in args.sweep_log2.split("-"))
+    for slots in (int(v) for v in args.sweep_slots.split(",")):
+        for channels in (int(v) for v in args.sweep_channels.split(",")):
+            for log2m in range(lo, hi + 1):
                 tokens = 1 << log2m
                 batch = tokens // (grid * grid)
                 units = algorithmic_units(slots)
@@ -357,21 +362,36 @@ def run_sweep(args, device, rank, world):
                 reps = max(3, min(50, (1 << 22) // tokens))
 
                 def timed(names):
+                    """ms per pass over `names`.  The launches of one rotation over the buffer sets are captured
+                    in a CUDA graph and the graph is replayed: at the small points a pass is a few 10 us of GPU work
+                    and would otherwise be bound by the host's launch calls, not by the kernels."""
                     for pth in paths:                                            # warm-up: every set once
                         for n in names:
                             getattr(pth, n)()
+                    torch.cuda.synchronize()
+                    side = torch.cuda.Stream()
+                    for pth in paths:
+                        pth.stream = side.cuda_stream
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=side):
+                        for pth in paths:
+                            for n in names:
+                                getattr(pth, n)()
+                    for pth in paths:
+                        pth.stream = torch.cuda.current_stream().cuda_stream
+                    rounds = max(1, -(-reps // nsets))
+                    graph.replay()
                     torch.cuda.synchronize()
                     if world > 1:
                         dist.barrier()
                     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     a.record()
-                    for r in range(reps):
-                        pth = paths[r % nsets]
-                        for n in names:
-                            getattr(pth, n)()
+                    for _ in range(rounds):
+                        graph.replay()
                     b.record()
                     torch.cuda.synchronize()
-                    ms = a.elapsed_time(b) / reps
+                    ms = a.elapsed_time(b) / (rounds * nsets)
+                    del graph
                     if world > 1:
                         t = torch.tensor([ms], device=device)
                         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -386,7 +406,7 @@ def run_sweep(args, device, rank, world):
                 tot = world * sum(units.values()) * unit / (fwd_ms + bwd_ms) / 1e6
                 if rank == 0:
                     print(json.dumps({"sweep": True, "n": slots, "channels": channels, "log2_tokens": log2m,
-                                      "n_gpus": world, "dtype": args.dtype, "buffer_sets": nsets,
+                                      "n_gpus": world, "dtype": args.dtype, "buffer_sets": nsets, "launch": "cuda graph",
                                       "fwd_ms": round(fwd_ms, 4), "bwd_ms": round(bwd_ms, 4),
                                       "fwd_GBs": round(fwd, 1), "bwd_GBs": round(bwd, 1), "fwd_bwd_GBs": round(tot, 1),
                                       "frac_of_peak": round(tot / world / peak, 4), "peak": peak,

@@ -78,6 +78,8 @@ def parse_args():
                     help="run the models' torch sublayers eagerly instead of under torch.compile")
     ap.add_argument("--train-impl", default="graph", choices=["graph", "compiled_ddp"],
                     help="SiHC-XL training step: this package's single-graph step, or whole-model compile + DDP")
+    ap.add_argument("--train-schedule", default="stage", choices=["stage", "literal"],
+                    help="single-graph step: factored stages with the stage-scoped backward, or the literal recurrence")
     ap.add_argument("--bucket-mb", type=int, default=256, help="gradient bucket size of the single-graph step")
     ap.add_argument("--no-overlap-optimizer", dest="overlap_optimizer", action="store_false",
                     help="single-graph step: one AdamW update after backward instead of per-bucket updates on the side "
@@ -564,7 +566,7 @@ def time_device(fn, steps, warmup, world, device):
 
 
 def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_steps=50, compile_model=True,
-                   train_impl="graph", bucket_mb=256, overlap_optimizer=False):
+                   train_impl="graph", bucket_mb=256, overlap_optimizer=False, train_schedule="stage"):
     """SiHC-B forward (batch 256), SiHC-XL training step (batch 32 per GPU, DDP) or SiHC-XL Heun sampling
     (batch 256 per GPU, CFG 2.4 on [0.1, 0.9]); bf16 autocast over fp32 parameters, synthetic N(0,1) images,
     random-init weights with opened gates.  Inputs start in pinned host memory every step.
@@ -612,7 +614,7 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         model = sihc_xl().to(device)
         model.open_gates()
         trainer = TrainStep(model, batch, lr=2e-4, betas=(0.9, 0.95), weight_decay=0.0, compile_model=compile_model,
-                            bucket_mb=bucket_mb, overlap_optimizer=overlap_optimizer)
+                            bucket_mb=bucket_mb, overlap_optimizer=overlap_optimizer, schedule=train_schedule)
         x_host = torch.randn(batch, 3, 256, 256, generator=gen).pin_memory()
         y = torch.randint(0, 1000, (batch,), device=device)
         trainer.step(x_host, y)                     # first eager pass: compiles the sublayers
@@ -631,8 +633,10 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         finally:
             trainer.close()        # the graph holds captured collectives: it must be gone before the group is destroyed
         name = ("SiHC-XL training step, 28 blocks x 1152, n=4, stages 8+12+8, batch 32 per GPU, bf16 autocast + fp32 AdamW, "
-                "one CUDA graph per step (stage-scoped backward, gradient all-reduce in %d MB buckets under backward%s)"
-                % (bucket_mb, ", per-bucket AdamW on the side stream" if overlap_optimizer else ""))
+                "one CUDA graph per step (%s, gradient all-reduce in %d MB buckets under backward%s)"
+                % ("factored stages with the stage-scoped backward" if train_schedule == "stage"
+                   else "literal schedule: fused write+read step and its fused adjoint",
+                   bucket_mb, ", per-bucket AdamW on the side stream" if overlap_optimizer else ""))
     elif kind == "sihc_xl_train":
         batch = 32
         model = sihc_xl().to(device)
@@ -813,7 +817,7 @@ def main():
         warm = max(args.warmup, 1) if args.workload == "sihc_xl_sample" else max(args.warmup, 3)
         res = model_workload(args.workload, device, rank, world, local_rank, args.steps, warm,
                              args.sample_steps, not args.no_compile, args.train_impl, args.bucket_mb,
-                             args.overlap_optimizer)
+                             args.overlap_optimizer, args.train_schedule)
         clocks = sampler.stop() if rank == 0 else None
         if rank == 0:
             print(json.dumps({"metric": args.workload + "_throughput", "value": res["img_per_s"], "unit": "img/s",
@@ -949,7 +953,8 @@ def main():
         for kind in (("sihc_xl_train", "sihc_b_fwd") if world == 1 else ("sihc_xl_train",)):
             try:
                 models[kind] = model_workload(kind, device, rank, world, local_rank, 20, 8, 50, cm,
-                                              args.train_impl, args.bucket_mb, args.overlap_optimizer)
+                                              args.train_impl, args.bucket_mb, args.overlap_optimizer,
+                                              args.train_schedule)
             except Exception as exc:                               # noqa: BLE001
                 if world > 1:
                     raise                                          # see above: never leave the peers waiting

@@ -96,6 +96,27 @@ int sihc_write_read_fwd(const void* x, const void* dz, const void* beta, const v
                         void* y, void* z_next, int64_t batch, int grid, int kh, int kw, int channels,
                         int dtype, int wdtype, void* stream);
 
+/* Scratch bytes for sihc_write_read_bwd. */
+size_t sihc_write_read_bwd_workspace_bytes(int64_t batch, int grid, int kh, int kw, int channels, int dtype);
+
+/*
+ * Backward of sihc_write_read_fwd, fused: with h = dL/dy and gz = dL/dz_next,
+ *   hh[m,s,c]          = h[m,s,c] + alpha_next[c,s] * gz[m,c]       (gradient w.r.t. x; rounded to `dtype`)
+ *   ddz[m,c]           = sum_s beta[c,s] * hh[m,s,c]                 (from the unrounded hh)
+ *   dweights[0][c,s]   = sum_m y[m,s,c] * gz[m,c]                    (dalpha_next, fp32)
+ *   dweights[1][c,s]   = sum_m dz[m,c] * hh[m,s,c]                   (dbeta, fp32)
+ * in one pass: 3*slots+3 elements per token and channel.  `y` is the carrier the forward call produced.  It is what
+ * differentiating the reference's literal schedule step `write_torch` -> `read_torch`
+ * (sihc/bench/fusion_controls.py:14-31, :64, :80) yields, which the reference leaves to autograd over separate
+ * operators.  `h` NULL = no gradient reaches y from later events (zero); `gz` NULL = the next read was unused
+ * (hh = h, dalpha_next = 0; `y` is then not read); `hh`, `ddz`, `dweights` may each be NULL to skip that output;
+ * `hh` may be `h` (in place).  `dweights` is [2, channels, slots] fp32.  Deterministic reduction as in sihc_read_bwd.
+ */
+int sihc_write_read_bwd(const void* h, const void* gz, const void* y, const void* dz, const void* beta,
+                        const void* alpha_next, void* hh, void* ddz, float* dweights, void* workspace,
+                        size_t workspace_bytes, int64_t batch, int grid, int kh, int kw, int channels,
+                        int dtype, int wdtype, void* stream);
+
 /*
  * Bytes of scratch the two backward entry points below need for `events` events
  * on this geometry (per-block partial sums of the weight gradients).  The

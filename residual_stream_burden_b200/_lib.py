@@ -25,6 +25,8 @@ SIGNATURES = {
     "sihc_read_fwd": (c_int, [c_void_p, c_void_p, POINTER(c_void_p), c_int] + _GEOM),
     "sihc_write_fwd": (c_int, [c_void_p, POINTER(c_void_p), c_void_p, c_void_p, c_int] + _GEOM),
     "sihc_write_read_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + _GEOM),
+    "sihc_write_read_bwd_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int, c_int]),
+    "sihc_write_read_bwd": (c_int, [c_void_p] * 9 + [c_void_p, c_size_t] + _GEOM),
     "sihc_wgrad_workspace_bytes": (c_size_t, [c_int, c_int64, c_int, c_int, c_int, c_int, c_int]),
     "sihc_read_bwd": (c_int, [c_void_p, POINTER(c_void_p), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int] + _GEOM),
     "sihc_read_bwd_static": (c_int, [c_void_p, POINTER(c_void_p), c_void_p, c_void_p, c_void_p, c_int] + _GEOM),

@@ -261,6 +261,35 @@ int sihc_write_read_fwd(const void* x, const void* dz, const void* beta, const v
     return status_of(launch_write_read(pb, x, dz, beta, alpha_next, y, z_next));
 }
 
+size_t sihc_write_read_bwd_workspace_bytes(int64_t batch, int grid, int kh, int kw, int channels, int dtype) {
+    return 2 * sihc_wgrad_workspace_bytes(1, batch, grid, kh, kw, channels, dtype);      // two row sets per block
+}
+
+int sihc_write_read_bwd(const void* h, const void* gz, const void* y, const void* dz, const void* beta,
+                        const void* alpha_next, void* hh, void* ddz, float* dweights, void* workspace,
+                        size_t workspace_bytes, int64_t batch, int grid, int kh, int kw, int channels, int dtype,
+                        int wdtype, void* stream) {
+    Problem pb;
+    if (int st = make_problem(pb, 1, batch, grid, kh, kw, channels, dtype, wdtype, stream)) return st;
+    if (!beta || !alpha_next) return SIHC_ERR_NULL;
+    if (gz && dweights && !y) return SIHC_ERR_NULL;          // dalpha_next needs the carrier
+    if (dweights && !dz) return SIHC_ERR_NULL;               // dbeta needs the update
+    if (!hh && !ddz && !dweights) return SIHC_OK;
+    VecChoice vc(vec_width(pb.dtype, pb.S), esize(dtype), pb.C);
+    vc.act(h); vc.act(gz); vc.act(y); vc.act(dz); vc.act(hh); vc.act(ddz);
+    vc.weight(beta, esize(wdtype)); vc.weight(alpha_next, esize(wdtype));
+    if (!vc.elem_ok || (dweights && !aligned(dweights, 4))) return SIHC_ERR_ALIGN;
+    pb.V = vc.V();
+    if (dweights)
+        if (int st = check_workspace(workspace, workspace_bytes, sihc_write_read_bwd_workspace_bytes(batch, grid, kh, kw, channels, dtype))) return st;
+    float* partial = dweights ? static_cast<float*>(workspace) : nullptr;
+    uint32_t blocks = 0;
+    cudaError_t e = launch_write_read_bwd(pb, h, gz, y, dz, beta, alpha_next, hh, ddz, partial, &blocks);
+    if (e == cudaSuccess && dweights)     // rows 0..S-1 -> dweights[0] (dalpha_next), rows S..2S-1 -> dweights[1] (dbeta)
+        e = launch_finish(partial, dweights, blocks, 2u * pb.S, pb.C, pb.S, pb.stream);
+    return status_of(e);
+}
+
 size_t sihc_wgrad_workspace_bytes(int events, int64_t batch, int grid, int kh, int kw, int channels, int dtype) {
     Problem pb;
     if (make_problem(pb, events, batch, grid, kh, kw, channels, dtype, dtype, nullptr)) return 0;

@@ -87,6 +87,11 @@ cudaError_t launch_tri_fwd(const Problem& pb, const void* base, const void* cons
 cudaError_t launch_tri_bwd(const Problem& pb, const void* grad, const void* const* dz, const void* gamma,
                            void* const* ddz, float* partial, uint32_t* blocks);
 
+// Fused backward of the literal step (sihc_literal.cu); `partial` receives [P][2S][C] rows (dalpha_next, then dbeta).
+cudaError_t launch_write_read_bwd(const Problem& pb, const void* h, const void* gz, const void* y, const void* dz,
+                                  const void* beta, const void* alpha_next, void* hh, void* ddz, float* partial,
+                                  uint32_t* blocks);
+
 // Whole-stage coefficient gradient dgamma[i][j][c] = sum_m g_i * dz_j (j < i; zero elsewhere), [E][E][C] fp32, from one
 // pass over the E-1 recorded gradients and E-1 updates (sihc_trigamma.cu).  Needs C * element size % 16 == 0 and
 // 16-byte aligned tensors.  g[0] and dz[E-1] are not read; a null g[i] gives a zero row.

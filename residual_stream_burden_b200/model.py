@@ -277,13 +277,15 @@ class SiHC(nn.Module):
             self.workspace_rope_incontext = AxialRope(half_head, workspace_grid, prefix_tokens=self.in_context_len)
         # "factored": one read, triangular accumulation, one write per stage (training and default).
         # "literal": write event i and read event i+1 in one pass over the carrier, no triangular step;
-        # forward-only, fewer bytes than the factored stage when n <= 4 (10 vs ~16 elements per event at E=24).
+        # fewer bytes than the factored stage when n <= 4 (10 vs ~16 elements per event at E=24).
         self.inference_schedule = "factored"
         # "per_op": every routing operator carries its own autograd formula (traceable by torch.compile).
         # "stage": the stage-scoped backward of :mod:`.stage` - lazily transposed triangular accumulation, one
         # gamma-gradient pass per stage; eager only (a Python tape), can be captured in a CUDA graph.
+        # "literal": the literal recurrence with the fused write+read step and its fused adjoint (traceable).
         self.training_schedule = "per_op"
         self.coefficients = SiHC.stage_coefficients
+        self.cast_coefficients = SiHC.cast_weights
         self.reset_parameters()
 
     def reset_parameters(self) -> None:
@@ -392,24 +394,32 @@ class SiHC(nn.Module):
             updates.append(dz)
         return ops.sublayer_write(x0, updates, beta), context
 
+    @staticmethod
+    def cast_weights(read_weights: Sequence[Tensor], write_weights: Sequence[Tensor], dtype: torch.dtype):
+        """``alpha, beta [N,C,S]``: every event's read / write weights in the carrier dtype, stacked (two tiny
+        kernels instead of two casts per event; a training step may swap in a compiled version)."""
+        return (torch.stack([w.to(dtype=dtype) for w in read_weights]).contiguous(),
+                torch.stack([w.to(dtype=dtype) for w in write_weights]).contiguous())
+
     def run_literal(self, carrier: Tensor, cond: Tensor, context: Tensor | None = None) -> Tensor:
         """All events with the literal recurrence (reference definition: ``literal_forward``,
-        research/tests/test_sublayer_kernels.py:216-226), each write fused with the next event's read."""
-        if torch.is_grad_enabled():
-            raise RuntimeError("the literal schedule is forward-only: call it under torch.no_grad()")
+        research/tests/test_sublayer_kernels.py:216-226), each write fused with the next event's read:
+        2S+2 elements per event forward and, through the fused adjoint of that step, 3S+3 backward - fewer bytes than
+        the factored stage when S <= 4 and a stage has many events.  The carrier is rounded to its storage dtype after
+        every event, exactly as the unfused path rounds it."""
         events, start = [], 0
         for size in self.stage_sizes:
             events += self.stage_events(self.blocks[start:start + size], cond, start)
             start += size
-        dtype = carrier.dtype
-        z = ops.sihc_read(carrier, events[0][0].alpha(dtype).contiguous())
-        for i, (conn, update, uses_context) in enumerate(events):
+        alpha, beta = self.cast_coefficients(tuple(c.read_weight for c, _, _ in events),
+                                             tuple(c.write_weight for c, _, _ in events), carrier.dtype)
+        z = ops.sihc_read(carrier, alpha[0])
+        for i, (_, update, uses_context) in enumerate(events):
             dz, context = self.apply_update(update, z, context, uses_context)
             if i + 1 < len(events):
-                carrier, z = ops.sihc_write_read(carrier, dz, conn.beta(dtype).contiguous(),
-                                                 events[i + 1][0].alpha(dtype).contiguous())
+                carrier, z = ops.sihc_write_read(carrier, dz, beta[i], alpha[i + 1])
             else:
-                carrier = ops.sihc_write(carrier, dz, conn.beta(dtype).contiguous())
+                carrier = ops.sihc_write(carrier, dz, beta[i])
         return carrier
 
     def initial_context(self, y_emb: Tensor, dtype) -> Tensor | None:
@@ -422,7 +432,8 @@ class SiHC(nn.Module):
         cond = self.t_embedder(t) + y_emb
         carrier = self.x_embedder(x)
         context = self.initial_context(y_emb, carrier.dtype)
-        if self.inference_schedule == "literal" and not torch.is_grad_enabled():
+        literal = self.training_schedule == "literal" if torch.is_grad_enabled() else self.inference_schedule == "literal"
+        if literal:
             carrier = self.run_literal(carrier, cond, context)
         else:
             start = 0

@@ -430,12 +430,12 @@ def sihc_write(x: Tensor, dz: Tensor, beta: Tensor) -> Tensor:
 
 @custom_op("sihc_b200::write_read", mutates_args=())
 def sihc_write_read(x: Tensor, dz: Tensor, beta: Tensor, alpha_next: Tensor) -> tuple[Tensor, Tensor]:
-    """One step of the literal schedule for inference: ``Y = X + beta * dz`` and the NEXT event's read
+    """One step of the literal schedule: ``Y = X + beta * dz`` and the NEXT event's read
     ``z = sum_s alpha_next * Y`` in a single pass over the carrier.  Returns ``(Y, z)``.
 
     ``beta`` and ``alpha_next`` are ``[C, S]``.  Same values as ``write_torch`` followed by ``read_torch``
     (sihc/bench/fusion_controls.py:14-31): the carrier is rounded to its storage dtype before it is read.
-    Forward only (no autograd formula): use it under ``torch.no_grad()``.
+    Differentiable in every argument: the backward is one fused pass (``sihc_write_read_bwd``).
     """
     if beta.ndim != 2 or alpha_next.ndim != 2 or beta.shape != alpha_next.shape or beta.dtype != alpha_next.dtype:
         raise ValueError("expected matching [channels, slots] write and read weights")
@@ -454,6 +454,62 @@ def sihc_write_read(x: Tensor, dz: Tensor, beta: Tensor, alpha_next: Tensor) -> 
 def _write_read_fake(x, dz, beta, alpha_next):
     b, c, g, _, _ = _validate_updates(x, beta.unsqueeze(0), [dz], fake=True)
     return torch.empty_like(x), x.new_empty((b, g * g, c))
+
+
+@custom_op("sihc_b200::write_read_backward", mutates_args=())
+def _write_read_backward_op(grad_y: Optional[Tensor], grad_z: Optional[Tensor], y: Tensor, dz: Tensor, beta: Tensor,
+                            alpha_next: Tensor, need_dx: bool, need_ddz: bool,
+                            need_dw: bool) -> tuple[Tensor, Tensor, Tensor]:
+    """All adjoints of :func:`sihc_write_read` in one pass: ``(dX, ddz, dweights)`` with
+    ``dX = grad_y + alpha_next * grad_z``, ``ddz = sum_s beta * dX``, ``dweights[0] = dalpha_next = sum_m Y * grad_z``
+    and ``dweights[1] = dbeta = sum_m dz * dX`` (fp32 accumulation, returned in the weights' dtype).  A missing
+    incoming gradient is ``None``; an output that is not needed comes back empty."""
+    b, c, g, kh, kw = _validate_updates(y, beta.unsqueeze(0), [dz])
+    for name, t, like in (("grad_y", grad_y, y), ("grad_z", grad_z, dz)):
+        if t is not None:
+            _require_packed("sublayer write/read backward", **{name: t})
+            if t.shape != like.shape or t.dtype != like.dtype or t.device != like.device:
+                raise ValueError(f"{name} does not match the forward output")
+    dx = torch.empty_like(y) if need_dx else y.new_empty(0)
+    ddz = torch.empty_like(dz) if need_ddz else dz.new_empty(0)
+    dw = torch.empty((2,) + tuple(beta.shape), device=y.device, dtype=torch.float32) if need_dw else beta.new_empty(0)
+    with torch.cuda.device(y.device):
+        nbytes = lib.sihc_write_read_bwd_workspace_bytes(b, g, kh, kw, c, _DTYPES[y.dtype]) if need_dw else 0
+        ws = _workspace(nbytes, y.device)
+        check(lib.sihc_write_read_bwd(None if grad_y is None else grad_y.data_ptr(),
+                                      None if grad_z is None else grad_z.data_ptr(), y.data_ptr(), dz.data_ptr(),
+                                      beta.data_ptr(), alpha_next.data_ptr(), dx.data_ptr() if need_dx else None,
+                                      ddz.data_ptr() if need_ddz else None, dw.data_ptr() if need_dw else None,
+                                      ws.data_ptr(), ws.numel(), b, g, kh, kw, c, _DTYPES[y.dtype], _DTYPES[beta.dtype],
+                                      _stream(y)), "sihc_write_read_bwd")
+    return dx, ddz, (dw.to(beta.dtype) if need_dw else dw)
+
+
+@_write_read_backward_op.register_fake
+def _write_read_backward_fake(grad_y, grad_z, y, dz, beta, alpha_next, need_dx, need_ddz, need_dw):
+    return (torch.empty_like(y) if need_dx else y.new_empty(0), torch.empty_like(dz) if need_ddz else dz.new_empty(0),
+            beta.new_empty((2,) + tuple(beta.shape)) if need_dw else beta.new_empty(0))
+
+
+def _write_read_setup(ctx, inputs, output):
+    _, dz, beta, alpha_next = inputs
+    ctx.save_for_backward(output[0], dz, beta, alpha_next)
+    ctx.set_materialize_grads(False)
+
+
+def _write_read_backward(ctx, grad_y, grad_z):
+    y, dz, beta, alpha_next = ctx.saved_tensors
+    need_x, need_u, need_b, need_a = ctx.needs_input_grad
+    if grad_y is None and grad_z is None:
+        return None, None, None, None
+    grad_y = None if grad_y is None else grad_y.contiguous()
+    grad_z = None if grad_z is None else grad_z.contiguous()
+    dx, ddz, dw = _write_read_backward_op(grad_y, grad_z, y, dz, beta, alpha_next, bool(need_x), bool(need_u),
+                                          bool(need_b or need_a))
+    return (dx if need_x else None), (ddz if need_u else None), (dw[1] if need_b else None), (dw[0] if need_a else None)
+
+
+register_autograd(sihc_write_read, _write_read_backward, setup_context=_write_read_setup)
 
 
 # --------------------------------------------------------------------------- block-wise adapters

@@ -59,6 +59,7 @@ def compile_sublayers(model: SiHC) -> SiHC:
     # casts, stacking and the gamma products of a stage's connection weights: one small compiled graph per stage
     # size instead of a few dozen tiny kernels (and as many again in backward)
     model.coefficients = torch.compile(SiHC.stage_coefficients, fullgraph=True, dynamic=False)
+    model.cast_coefficients = torch.compile(SiHC.cast_weights, fullgraph=True, dynamic=False)
     return model
 
 
@@ -69,17 +70,22 @@ class TrainStep:
     ``force_exchange`` asks for its collectives anyway).  ``bucket_mb`` sizes the gradient buckets;
     ``overlap_optimizer`` runs each bucket's AdamW update on the side stream right after its all-reduce instead of
     one update after backward.  ``use_graph=False`` runs the same step eagerly (for tests and debugging).
+    ``schedule``: ``"stage"`` = the reference's factored stages with the stage-scoped backward; ``"literal"`` = the
+    literal recurrence with the fused write+read step and its fused adjoint (fewer bytes when n <= 4).
     """
 
     def __init__(self, model: SiHC, batch: int, *, lr: float = 2e-4, betas=(0.9, 0.95), weight_decay: float = 0.0,
                  group=None, bucket_mb: float = 256, in_place_exchange: bool = True, overlap_optimizer: bool = False,
-                 compile_model: bool = True, use_graph: bool = True, force_exchange: bool = False, warmup: int = 3):
+                 compile_model: bool = True, use_graph: bool = True, force_exchange: bool = False, warmup: int = 3,
+                 schedule: str = "stage"):
         device = next(model.parameters()).device
         if device.type != "cuda":
             raise ValueError("TrainStep needs the model on a CUDA device")
         self.model, self.device, self.use_graph = model, device, use_graph
+        if schedule not in ("stage", "literal"):
+            raise ValueError("schedule must be 'stage' (factored stages, stage-scoped backward) or 'literal'")
         model.train()
-        model.training_schedule = "stage"
+        model.training_schedule = schedule
         if compile_model:
             compile_sublayers(model)
         self.stream = torch.cuda.Stream(device)

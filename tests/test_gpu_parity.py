@@ -649,3 +649,46 @@ def test_stage_coefficient_gradient_in_one_pass(events, tokens, c, dtype):
         rel = (got - want).norm() / want.norm()
         assert rel <= 1e-5, float(rel)                     # fp32 accumulation of exact products
         torch.testing.assert_close(got, want, atol=2e-4 * tokens ** 0.5, rtol=2e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("slots,b,g,c,wf32", [(4, 4, 16, 768, False), (4, 3, 7, 67, False), (2, 2, 5, 64, False),
+                                              (8, 2, 6, 128, False), (16, 2, 4, 64, False), (4, 2, 6, 1152, True)])
+def test_fused_adjoint_of_the_write_then_read_step(R, slots, b, g, c, wf32, dtype):
+    """Every gradient of sihc_write_read (carrier, update, beta, alpha_next) from the fused 3S+3 pass, against fp64
+    autograd through the oracle's write followed by read, and against this library's separate operators."""
+    if wf32 and dtype == torch.float32:
+        pytest.skip("fp32 weights over fp32 tensors is the plain fp32 case")
+    torch.manual_seed(61 + slots + c)
+    kh, kw = O.cell_shape(slots)
+    wdt = torch.float32 if wf32 else dtype
+    x = torch.randn(b, g * kh, g * kw, c).to(dtype)
+    dz = torch.randn(b, g * g, c).to(dtype)
+    beta = (1.0 + 0.05 * torch.randn(c, slots)).to(wdt)
+    alpha = (1.0 / slots + 0.05 * torch.randn(c, slots)).to(wdt)
+    gy = torch.randn_like(x)
+    gz = torch.randn_like(dz)
+    dev = [t.to(DEV).requires_grad_() for t in (x, dz, beta, alpha)]
+    y, z = R.sihc_write_read(*dev)
+    got = torch.autograd.grad((y, z), dev, (gy.to(DEV), gz.to(DEV)))
+    ref = [t.double().requires_grad_() for t in (x, dz, beta, alpha)]
+
+    def stored(t):          # the unfused path stores the carrier in `dtype` before the read sees it; the rounding is
+        return t + (t.to(dtype).double() - t).detach()      # applied to the value only (gradients pass unrounded)
+
+    oy = stored(O.write(ref[0], [ref[1]], [ref[2]], acc=torch.float64))
+    oz = O.read(oy, ref[3], acc=torch.float64)
+    want = torch.autograd.grad((oy, oz), ref, (gy.double(), gz.double()))
+    for name, a, w in zip(("dx", "ddz", "dbeta", "dalpha_next"), got, want):
+        close(a, w.to(a.dtype), dtype, name)
+    # only one incoming gradient: the other side is treated as zero
+    only_y = torch.autograd.grad(R.sihc_write_read(*dev)[0], dev[:3], gy.to(DEV))
+    want_y = torch.autograd.grad(O.write(ref[0], [ref[1]], [ref[2]], acc=torch.float64), ref[:3], gy.double())
+    assert torch.equal(only_y[0], gy.to(DEV))
+    close(only_y[1], want_y[1].to(dtype), dtype, "ddz (carrier gradient only)")
+    close(only_y[2], want_y[2].to(wdt), dtype, "dbeta (carrier gradient only)")
+    only_z = torch.autograd.grad(R.sihc_write_read(*dev)[1], dev, gz.to(DEV))
+    oy2 = stored(O.write(ref[0], [ref[1]], [ref[2]], acc=torch.float64))
+    want_z = torch.autograd.grad(O.read(oy2, ref[3], acc=torch.float64), ref, gz.double())
+    for name, a, w in zip(("dx", "ddz", "dbeta", "dalpha_next"), only_z, want_z):
+        close(a, w.to(a.dtype), dtype, name + " (read gradient only)")

@@ -35,8 +35,8 @@ def assert_same_training(model, ref, init):
         assert float(apart) <= 0.05 * float(travelled), (name, float(apart), float(travelled))
 
 
-def eager_reference(model, images, labels, steps):
-    model.training_schedule = "stage"          # same routing arithmetic as the captured step
+def eager_reference(model, images, labels, steps, schedule="stage"):
+    model.training_schedule = schedule         # same routing arithmetic as the captured step
     opt = torch.optim.AdamW(model.parameters(), lr=2e-4, betas=(0.9, 0.95), weight_decay=0.0, fused=True)
     losses = []
     for k in range(steps):
@@ -51,9 +51,10 @@ def eager_reference(model, images, labels, steps):
     return losses
 
 
-@pytest.mark.parametrize("overlap_optimizer", [False, True])
-@pytest.mark.parametrize("compile_model", [False, True])
-def test_captured_step_matches_eager_training_loop(monkeypatch, compile_model, overlap_optimizer):
+@pytest.mark.parametrize("schedule,overlap_optimizer,compile_model", [("stage", False, False), ("stage", True, False),
+                                                                      ("stage", False, True), ("stage", True, True),
+                                                                      ("literal", True, False), ("literal", True, True)])
+def test_captured_step_matches_eager_training_loop(monkeypatch, schedule, compile_model, overlap_optimizer):
     import residual_stream_burden_b200.train as T
     from residual_stream_burden_b200.model import SublayerSiHC
     monkeypatch.setattr(T, "velocity_training_batch", fixed_noise_batch)
@@ -65,10 +66,10 @@ def test_captured_step_matches_eager_training_loop(monkeypatch, compile_model, o
     steps, batch = 6, 2
     images = [torch.randn(batch, 3, 256, 256, device="cuda") for _ in range(steps)]
     labels = torch.tensor([3, 977], device="cuda")
-    want = eager_reference(ref, images, labels, steps)
+    want = eager_reference(ref, images, labels, steps, schedule)
 
     with T.TrainStep(model, batch, compile_model=compile_model, overlap_optimizer=overlap_optimizer,
-                     bucket_mb=0.05, warmup=2) as trainer:
+                     bucket_mb=0.05, warmup=2, schedule=schedule) as trainer:
         got = [float(trainer.step(images[k], labels)) for k in range(steps)]
         assert trainer.graph is not None                          # steps 3.. ran as graph replays
         if overlap_optimizer:

@@ -98,11 +98,12 @@ inline cudaError_t launch_persistent(K kernel, P& params, const Problem& pb, int
 // The block is shrunk (fewer token lanes) until its ring fits the 227 KB a block may use.
 template <typename K, typename P>
 inline cudaError_t launch_persistent_smem(K kernel, P& params, const Problem& pb, int V, int default_threads,
-                                          size_t smem_per_thread, bool emits_partials, uint32_t* gx_out) {
+                                          size_t smem_per_thread, bool emits_partials, uint32_t* gx_out,
+                                          int max_threads = kMaxThreads) {
     constexpr size_t kMaxDynamic = 200 * 1024;     // leaves room for the static reduction buffer
     const Tuning& tn = tuning();
     const uint32_t ncv = pb.C / static_cast<uint32_t>(V);
-    BlockShape bs = block_shape(ncv, tn.threads > 0 ? tn.threads : default_threads);
+    BlockShape bs = block_shape(ncv, tn.threads > 0 ? tn.threads : default_threads, max_threads);
     while (bs.tl > 1 && static_cast<size_t>(bs.threads) * smem_per_thread > kMaxDynamic) { --bs.tl; bs.threads = bs.cl * bs.tl; }
     const size_t smem = static_cast<size_t>(bs.threads) * smem_per_thread;
     if (smem > kMaxDynamic) return cudaErrorInvalidConfiguration;

@@ -14,6 +14,7 @@
 // over a persistent grid, keeps 2*S*V fp32 accumulators, and the block leaves one fp32 row set
 // [dalpha rows 0..S-1, dbeta rows S..2S-1] in scratch; a fixed-order finishing pass sums the blocks.
 #include "sihc_dispatch.cuh"
+#include "sihc_ring.cuh"
 
 namespace sihc {
 
@@ -134,6 +135,144 @@ __global__ void __launch_bounds__(kLiteralBwdThreads) write_read_bwd_kernel(cons
     }
 }
 
+
+// The same pass with its 2S+2 input vectors per token staged through a per-thread `cp.async` ring in shared memory
+// (NST stages, private slots, no block barrier - the scheme of the single-event adjoints in sihc_ring.cu).  The
+// register-staged kernel above holds 2*S*V accumulators and 2*S*V coefficients and has no registers left to keep a
+// second token's loads in flight; here the loads never occupy registers while they travel.  Vector path only.
+constexpr int kLiteralRingThreads = 256;       // target; whole channel rows round it to at most kLiteralRingMaxThreads
+constexpr int kLiteralRingMaxThreads = 320;
+constexpr int kLiteralRingStages = 3;
+// Half-width form: V/2 channels per thread, twice the threads (and warps) for the same bytes in flight.
+constexpr int kLiteralHalfThreads = 512;
+constexpr int kLiteralHalfMaxThreads = 576;
+
+template <typename T, typename W, int S, int V, int NST, int MAXT>
+__global__ void __launch_bounds__(MAXT) write_read_bwd_ring_kernel(const __grid_constant__ WriteReadBwdParams p) {
+    typedef VecIO<T, V> IO;
+    typedef typename IO::Raw Raw;
+    constexpr int VB = int(sizeof(Raw));
+    constexpr int NV = 2 * S + 2;                 // h slots, y slots, gz, dz
+    extern __shared__ __align__(16) unsigned char ring_bytes[];
+    __shared__ float red[MAXT * V];
+    const Tiling& t = p.t;
+    const Lane ln = make_lane<V>(t);
+    const Ring<Raw> ring{reinterpret_cast<Raw*>(ring_bytes), blockDim.x, threadIdx.x, NV};
+    const T* h = p.h ? static_cast<const T*>(p.h) + ln.c0 : nullptr;
+    const T* __restrict__ gz = p.gz ? static_cast<const T*>(p.gz) + ln.c0 : nullptr;
+    const T* __restrict__ y = p.y ? static_cast<const T*>(p.y) + ln.c0 : nullptr;
+    const T* __restrict__ dz = p.dz ? static_cast<const T*>(p.dz) + ln.c0 : nullptr;
+    T* hh = p.hh ? static_cast<T*>(p.hh) + ln.c0 : nullptr;
+    T* __restrict__ ddz = p.ddz ? static_cast<T*>(p.ddz) + ln.c0 : nullptr;
+    const bool want_w = p.partial != nullptr;
+    const bool want_y = gz != nullptr && want_w && y != nullptr;
+    const bool want_dz = dz != nullptr && want_w;
+    constexpr bool kPacked = std::is_same<T, W>::value && sizeof(T) == 2;
+    float wa[kPacked ? 1 : S][V], wb[kPacked ? 1 : S][V], da[S][V], db[S][V], kappa[V];
+    Raw war[kPacked ? S : 1], wbr[kPacked ? S : 1];
+#pragma unroll
+    for (int s = 0; s < S; ++s)
+#pragma unroll
+        for (int v = 0; v < V; ++v) { da[s][v] = 0.f; db[s][v] = 0.f; }
+#pragma unroll
+    for (int v = 0; v < V; ++v) kappa[v] = 0.f;
+    if (ln.active) {
+        {
+            float fa[S][V], fb[S][V];
+            load_coeffs<W, S, V>(static_cast<const W*>(p.alpha) + static_cast<size_t>(ln.c0) * S, fa);
+            load_coeffs<W, S, V>(static_cast<const W*>(p.beta) + static_cast<size_t>(ln.c0) * S, fb);
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                if constexpr (kPacked) {
+                    war[s] = IO::pack(fa[s]); wbr[s] = IO::pack(fb[s]);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) kappa[v] = fmaf(fa[s][v], fb[s][v], kappa[v]);
+                } else {
+#pragma unroll
+                    for (int v = 0; v < V; ++v) { wa[s][v] = fa[s][v]; wb[s][v] = fb[s][v]; }
+                }
+            }
+        }
+        // `src_or` keeps the address valid when a copy is switched off (zero source bytes = zero fill)
+        const T* const src_or = static_cast<const T*>(p.beta ? p.beta : p.alpha);
+        auto issue = [&](uint32_t tile, int stage) {
+            const uint32_t m = tile * t.tl + ln.tl;
+            const bool ok = tile < t.ntiles && m < t.M;
+            const uint32_t mm = ok ? m : 0u;
+            const size_t origin = cell_origin<S>(mm, t.g, t.C);
+            const size_t row = static_cast<size_t>(mm) * t.C;
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                const size_t off = origin + slot_offset<S>(s, t.g, t.C);
+                cp_async<VB>(ring.slot(stage, s), h != nullptr ? h + off : src_or, ok && h != nullptr);
+                cp_async<VB>(ring.slot(stage, S + s), want_y ? y + off : src_or, ok && want_y);
+            }
+            cp_async<VB>(ring.slot(stage, 2 * S), gz != nullptr ? gz + row : src_or, ok && gz != nullptr);
+            cp_async<VB>(ring.slot(stage, 2 * S + 1), want_dz ? dz + row : src_or, ok && want_dz);
+            cp_async_commit();
+        };
+        uint32_t tile = blockIdx.x;
+#pragma unroll
+        for (int st = 0; st < NST - 1; ++st) issue(tile + st * gridDim.x, st);
+        int stage = 0;
+        for (; tile < t.ntiles; tile += gridDim.x) {
+            cp_async_wait<NST - 2>();
+            Raw hr[S], yr[S];
+#pragma unroll
+            for (int s = 0; s < S; ++s) { hr[s] = *ring.slot(stage, s); yr[s] = *ring.slot(stage, S + s); }
+            const Raw gr = *ring.slot(stage, 2 * S);
+            const Raw dr = *ring.slot(stage, 2 * S + 1);
+            issue(tile + (NST - 1) * gridDim.x, stage == 0 ? NST - 1 : stage - 1);
+            const uint32_t m = tile * t.tl + ln.tl;
+            const bool ok = m < t.M;
+            const size_t origin = cell_origin<S>(ok ? m : 0u, t.g, t.C);
+            float gv[V], dv[V], zacc[V];
+            IO::unpack(gr, gv);
+            IO::unpack(dr, dv);
+            if constexpr (kPacked) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) zacc[v] = kappa[v] * gv[v];
+#pragma unroll
+                for (int s = 0; s < S; ++s) {
+                    float hv[V];
+                    IO::unpack(hr[s], hv);
+                    IO::fma_raw(wbr[s], hr[s], zacc);
+                    IO::fma_raw(war[s], gr, hv);
+                    IO::fma_raw(yr[s], gr, da[s]);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) db[s][v] = fmaf(dv[v], hv[v], db[s][v]);
+                    if (hh != nullptr && ok) IO::store(hh + origin + slot_offset<S>(s, t.g, t.C), hv);
+                }
+            } else {
+#pragma unroll
+                for (int v = 0; v < V; ++v) zacc[v] = 0.f;
+#pragma unroll
+                for (int s = 0; s < S; ++s) {
+                    float hv[V], yv[V];
+                    IO::unpack(hr[s], hv);
+                    IO::unpack(yr[s], yv);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        hv[v] = fmaf(wa[s][v], gv[v], hv[v]);
+                        da[s][v] = fmaf(yv[v], gv[v], da[s][v]);
+                        db[s][v] = fmaf(dv[v], hv[v], db[s][v]);
+                        zacc[v] = fmaf(wb[s][v], hv[v], zacc[v]);
+                    }
+                    if (hh != nullptr && ok) IO::store(hh + origin + slot_offset<S>(s, t.g, t.C), hv);
+                }
+            }
+            if (ddz != nullptr && ok) IO::store(ddz + static_cast<size_t>(m) * t.C, zacc);
+            stage = stage + 1 == NST ? 0 : stage + 1;
+        }
+        cp_async_wait<0>();
+    }
+    if (want_w) {
+        float* dst = p.partial + static_cast<size_t>(blockIdx.x) * 2 * S * t.C;
+        block_reduce_rows<S, V>(da, dst, t.C, ln.c0, ln.cl, ln.tl, t.cl, t.tl, ln.active, red);
+        block_reduce_rows<S, V>(db, dst + static_cast<size_t>(S) * t.C, t.C, ln.c0, ln.cl, ln.tl, t.cl, t.tl, ln.active, red);
+    }
+}
+
 cudaError_t launch_write_read_bwd(const Problem& pb, const void* h, const void* gz, const void* y, const void* dz,
                                   const void* beta, const void* alpha_next, void* hh, void* ddz, float* partial,
                                   uint32_t* blocks) {
@@ -147,6 +286,29 @@ cudaError_t launch_write_read_bwd(const Problem& pb, const void* h, const void* 
             if (pb.V == 1)
                 return launch_persistent(write_read_bwd_kernel<T, W, S, 1>, p, pb, 1, 1, kLiteralBwdThreads, 1,
                                          partial != nullptr, blocks, kLiteralBwdThreads);
+            // In place (hh == h) the carrier gradient must be read with coherent loads: the ring's asynchronous copies
+            // go through L2 and a thread only rewrites what it has already consumed, so the ring form covers it too.
+            const int ring = tuning().ring;       // 0 = register-staged form, otherwise the ring (default)
+            if constexpr (VM * int(sizeof(T)) >= 4) {
+                constexpr int VH = (S * VM >= 32 && VM * int(sizeof(T)) >= 8) ? VM / 2 : VM;
+                if (ring != 0 && tuning().half_vectors != 0 && VH != VM) {
+                    return launch_persistent_smem(write_read_bwd_ring_kernel<T, W, S, VH, kLiteralRingStages, kLiteralHalfMaxThreads>,
+                                                  p, pb, VH, kLiteralHalfThreads,
+                                                  static_cast<size_t>(kLiteralRingStages) * (2 * S + 2) * VH * sizeof(T),
+                                                  partial != nullptr, blocks, kLiteralHalfMaxThreads);
+                }
+                if (ring >= 4) {
+                    return launch_persistent_smem(write_read_bwd_ring_kernel<T, W, S, VM, 4, kLiteralRingMaxThreads>, p, pb, VM,
+                                                  kLiteralRingThreads, static_cast<size_t>(4) * (2 * S + 2) * VM * sizeof(T),
+                                                  partial != nullptr, blocks, kLiteralRingMaxThreads);
+                }
+                if (ring != 0) {
+                    return launch_persistent_smem(write_read_bwd_ring_kernel<T, W, S, VM, kLiteralRingStages, kLiteralRingMaxThreads>,
+                                                  p, pb, VM, kLiteralRingThreads,
+                                                  static_cast<size_t>(kLiteralRingStages) * (2 * S + 2) * VM * sizeof(T),
+                                                  partial != nullptr, blocks, kLiteralRingMaxThreads);
+                }
+            }
             return launch_persistent(write_read_bwd_kernel<T, W, S, VM>, p, pb, VM, 1, kLiteralBwdThreads, 1,
                                      partial != nullptr, blocks, kLiteralBwdThreads);
         });

@@ -651,10 +651,19 @@ def test_stage_coefficient_gradient_in_one_pass(events, tokens, c, dtype):
         torch.testing.assert_close(got, want, atol=2e-4 * tokens ** 0.5, rtol=2e-4)
 
 
+@pytest.fixture(params=[-1, 0], ids=["ring", "register-staged"])
+def adjoint_form(request):
+    """Both forms of the fused adjoint: loads staged through the async-copy ring (default) or through registers."""
+    from residual_stream_burden_b200 import _lib
+    _lib.tune("ring_stages", request.param)
+    yield request.param
+    _lib.tune("ring_stages", -1)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("slots,b,g,c,wf32", [(4, 4, 16, 768, False), (4, 3, 7, 67, False), (2, 2, 5, 64, False),
                                               (8, 2, 6, 128, False), (16, 2, 4, 64, False), (4, 2, 6, 1152, True)])
-def test_fused_adjoint_of_the_write_then_read_step(R, slots, b, g, c, wf32, dtype):
+def test_fused_adjoint_of_the_write_then_read_step(R, adjoint_form, slots, b, g, c, wf32, dtype):
     """Every gradient of sihc_write_read (carrier, update, beta, alpha_next) from the fused 3S+3 pass, against fp64
     autograd through the oracle's write followed by read, and against this library's separate operators."""
     if wf32 and dtype == torch.float32:

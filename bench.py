@@ -476,6 +476,19 @@ def run_stage_ops(args, device, steps, warmup):
     peak, peak_kind = load_peaks()
     res = {}
     launches0 = _lib.launch_count()
+    # write-only bandwidth of the device (16-byte streaming stores, 1 GiB): the bound for mostly-output operators
+    probe = torch.empty(1 << 30, dtype=torch.uint8, device=device)
+    for _ in range(3):
+        _lib.check(lib.sihc_probe_store_stream(probe.data_ptr(), probe.numel(), st), "store stream")
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(10):
+        lib.sihc_probe_store_stream(probe.data_ptr(), probe.numel(), st)
+    b.record()
+    torch.cuda.synchronize()
+    store_gbs = probe.numel() * 10 / a.elapsed_time(b) / 1e6
+    del probe
     for name, (fn, units) in ops.items():
         for _ in range(warmup):
             _lib.check(fn(), name)
@@ -502,7 +515,8 @@ def run_stage_ops(args, device, steps, warmup):
                       "steps": steps, "warmup": warmup, "ms_per_step": round(total_ms, 4), "higher_is_better": True,
                       "dtype": args.dtype, "data": "synthetic",
                       "config": {"workload": f"stage operators, E={E} events, n={S}, width {C}, {tokens} tokens"},
-                      "peak": peak, "peak_source": peak_kind, "ops": res, "comparators": comparators,
+                      "peak": peak, "peak_source": peak_kind, "store_stream_GBs": round(store_gbs, 1), "ops": res,
+                      "comparators": comparators,
                       "gpu_launches": int(_lib.launch_count() - launches0)}))
 
 

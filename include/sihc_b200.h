@@ -245,6 +245,14 @@ int sihc_tri_dgamma(const void* const* g, const void* const* dz, float* dgamma, 
  */
 int sihc_tune(const char* name, int value);
 
+/*
+ * Measurement aid, no counterpart in the reference: fill `bytes` (a multiple of 16, `dst` 16-byte aligned) with zeros
+ * using the 16-byte streaming stores of the routing kernels and nothing else.  Its bandwidth is the device's
+ * write-only rate, the bound for operators whose traffic is mostly output (a 24-event stage read writes 24 of its
+ * 28 elements per token and channel).
+ */
+int sihc_probe_store_stream(void* dst, size_t bytes, void* stream);
+
 /* Number of kernel launches this library has issued in this process (for benches). */
 uint64_t sihc_launch_count(void);
 

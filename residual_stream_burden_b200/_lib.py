@@ -39,6 +39,7 @@ SIGNATURES = {
     "sihc_tri_dgamma": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_void_p, c_void_p, c_size_t, c_int, c_int64, c_int,
                                 c_int, c_void_p]),
     "sihc_tune": (c_int, [c_char_p, c_int]),
+    "sihc_probe_store_stream": (c_int, [c_void_p, c_size_t, c_void_p]),
     "sihc_launch_count": (c_uint64, []),
 }
 

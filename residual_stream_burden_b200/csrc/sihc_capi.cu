@@ -220,6 +220,13 @@ int sihc_tune(const char* name, int value) {
 
 uint64_t sihc_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+int sihc_probe_store_stream(void* dst, size_t bytes, void* stream) {
+    if (!dst) return SIHC_ERR_NULL;
+    if (!aligned(dst, 16) || bytes % 16 != 0) return SIHC_ERR_ALIGN;
+    if (bytes == 0) return SIHC_OK;
+    return status_of(launch_store_stream(dst, bytes, static_cast<cudaStream_t>(stream)));
+}
+
 int sihc_read_fwd(const void* x, const void* alpha, void* const* out, int events, int64_t batch, int grid, int kh,
                   int kw, int channels, int dtype, int wdtype, void* stream) {
     Problem pb;

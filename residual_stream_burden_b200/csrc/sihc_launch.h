@@ -100,6 +100,9 @@ size_t tri_dgamma_workspace_bytes(int E, uint32_t M, uint32_t C, size_t esize);
 cudaError_t launch_tri_dgamma(const Problem& pb, const void* const* g, const void* const* dz, float* partial,
                               float* dgamma);
 
+// Measurement aid: write `bytes` of zeros with the same 16-byte streaming stores the kernels use (sihc_reduce.cu).
+cudaError_t launch_store_stream(void* dst, size_t bytes, cudaStream_t stream);
+
 // ---- shared launch plumbing -------------------------------------------------------------------
 struct BlockShape { uint32_t cl, tl, gy, threads; };
 

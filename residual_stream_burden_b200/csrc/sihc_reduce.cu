@@ -268,6 +268,22 @@ __global__ void __launch_bounds__(kMaxThreads) tri_bwd_kernel(const __grid_const
     }
 }
 
+// ---- store-stream probe -------------------------------------------------------------------------
+// Nothing but 16-byte `st.global.cs` stores over a persistent grid: the write-only bandwidth of the device, which is
+// what bounds kernels whose traffic is mostly output (the 24-event stage read writes 24 of its 28 elements).
+__global__ void __launch_bounds__(512) store_stream_kernel(uint4* __restrict__ dst, size_t vectors) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < vectors; i += stride)
+        st_stream(dst + i, make_uint4(0u, 0u, 0u, 0u));
+}
+
+cudaError_t launch_store_stream(void* dst, size_t bytes, cudaStream_t stream) {
+    const int nb = occupancy_blocks(store_stream_kernel, 512);
+    store_stream_kernel<<<static_cast<uint32_t>(sm_count() * nb), 512, 0, stream>>>(static_cast<uint4*>(dst), bytes / 16);
+    count_launch();
+    return cudaGetLastError();
+}
+
 // ---- host launchers ------------------------------------------------------------------------------
 namespace {
 constexpr int kTT = 2;

@@ -53,11 +53,32 @@ def allreduce_weight_grads(grads: Sequence[Tensor], group=None, average: bool = 
         offset += n
 
 
+def observe_ready_order(params: Sequence[torch.nn.Parameter], run_backward) -> list:
+    """The parameters in the order their gradients are accumulated when ``run_backward()`` runs one backward pass
+    (parameters that received no gradient come last, in reverse registration order).  Deterministic for a fixed
+    model and schedule, so every rank derives the same order.  The caller clears the gradients afterwards."""
+    params = [p for p in params if p.requires_grad]
+    order: list = []
+    handles = [p.register_post_accumulate_grad_hook(order.append) for p in params]
+    try:
+        run_backward()
+    finally:
+        for h in handles:
+            h.remove()
+    seen = {id(p) for p in order}
+    return order + [p for p in reversed(params) if id(p) not in seen]
+
+
 class BucketedGradExchange:
     """Data-parallel gradient averaging that runs UNDER the backward pass instead of after it.
 
-    The parameters are grouped into buckets in the order their gradients become final during backward (the
-    reverse of the order in which the model registered them).  A hook on every parameter counts its bucket down;
+    The parameters are grouped into buckets in the order their gradients become final during backward: the order
+    observed in a real backward pass (:func:`observe_ready_order`, ``ready_order=True``) or, failing that, the reverse
+    of the order in which the model registered them.  The observed order matters: the small connection weights of a
+    SiHC stage, for instance, are registered with their blocks but receive their gradients only when the backward of
+    the whole stage (or, in the literal schedule, of the whole model) has finished, and a bucket cannot be reduced
+    before its last gradient - with registration order every bucket would wait for the very end of backward.
+    A hook on every parameter counts its bucket down;
     when a bucket's last gradient has been accumulated its all-reduce is issued at once on a side stream, so it
     overlaps the backward kernels of the layers below.  :meth:`finish` makes the calling stream wait for all of
     them.  This is the role ``DistributedDataParallel`` plays in the reference trainer
@@ -76,7 +97,7 @@ class BucketedGradExchange:
 
     def __init__(self, params: Sequence[torch.nn.Parameter], group=None, bucket_bytes: int = 256 << 20,
                  in_place: bool = True, small_numel: int = 1 << 16, comm_stream=None, force: bool = False,
-                 on_bucket_reduced=None):
+                 on_bucket_reduced=None, ready_order: bool = False):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
         self.active = self.world > 1 or (force and dist.is_available() and dist.is_initialized())
@@ -85,7 +106,7 @@ class BucketedGradExchange:
         params = [p for p in params if p.requires_grad]
         self.buckets: list[list[torch.nn.Parameter]] = []
         current, size = [], 0
-        for p in reversed(params):                       # backward order
+        for p in (params if ready_order else reversed(params)):          # the order the gradients become ready
             current.append(p)
             size += p.numel() * p.element_size()
             if size >= bucket_bytes:

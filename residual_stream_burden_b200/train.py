@@ -31,7 +31,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
-from .dist import BucketedGradExchange
+from .dist import BucketedGradExchange, observe_ready_order
 from .model import Branch, SiHC, velocity_training_batch
 
 
@@ -92,24 +92,44 @@ class TrainStep:
         self.images = torch.zeros(batch, model.in_channels, model.input_size, model.input_size, device=device)
         self.labels = torch.zeros(batch, dtype=torch.long, device=device)
         self.loss = torch.zeros((), device=device)
-        params = [p for p in model.parameters() if p.requires_grad]
-        distributed = dist.is_available() and dist.is_initialized()
+        # The gradient buckets and the optimizer(s) are built at the first step, after one probe backward pass has
+        # shown the order in which the gradients become ready (see _setup).
+        self._exchange_kw = dict(group=group, bucket_bytes=int(bucket_mb * (1 << 20)), in_place=in_place_exchange,
+                                 force=force_exchange)
+        self._opt_kw = dict(lr=lr, betas=betas, weight_decay=weight_decay, fused=True, capturable=use_graph)
+        self._overlap_optimizer = overlap_optimizer
         self.exchange: Optional[BucketedGradExchange] = None
-        opt_kw = dict(lr=lr, betas=betas, weight_decay=weight_decay, fused=True, capturable=use_graph)
         self.bucket_optimizers = None
-        if distributed or overlap_optimizer:
-            self.exchange = BucketedGradExchange(params, group=group, bucket_bytes=int(bucket_mb * (1 << 20)),
-                                                 in_place=in_place_exchange, force=force_exchange,
-                                                 on_bucket_reduced=self._bucket_ready if overlap_optimizer else None)
-        if overlap_optimizer:
-            self.bucket_optimizers = [torch.optim.AdamW(bucket, **opt_kw) for bucket in self.exchange.buckets]
-            self.optimizer = None
-        else:
-            self.optimizer = torch.optim.AdamW(params, **opt_kw)
+        self.optimizer = None
+        self._ready = False
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._warmup_left = max(int(warmup), 1 if use_graph else 0)
 
     # ---- the step body (runs eagerly during warm-up, once more under capture, never again after) -------------
+    def _setup(self) -> None:
+        """One probe forward + backward on the staged inputs (no update) to observe the order in which the gradients
+        become ready; then the buckets follow that order and the optimizers are created."""
+        params = [p for p in self.model.parameters() if p.requires_grad]
+
+        def probe():
+            z, t, v = velocity_training_batch(self.images)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                pred = self.model(z, t, self.labels)
+            (pred.float() - v).square().mean().backward()
+
+        order = observe_ready_order(params, probe)
+        self._zero_grad()
+        distributed = dist.is_available() and dist.is_initialized()
+        if distributed or self._overlap_optimizer:
+            self.exchange = BucketedGradExchange(order, ready_order=True,
+                                                 on_bucket_reduced=self._bucket_ready if self._overlap_optimizer else None,
+                                                 **self._exchange_kw)
+        if self._overlap_optimizer:
+            self.bucket_optimizers = [torch.optim.AdamW(bucket, **self._opt_kw) for bucket in self.exchange.buckets]
+        else:
+            self.optimizer = torch.optim.AdamW(params, **self._opt_kw)
+        self._ready = True
+
     def _bucket_ready(self, k: int) -> None:
         self.bucket_optimizers[k].step()           # on the side stream, right behind the bucket's all-reduce
 
@@ -151,6 +171,8 @@ class TrainStep:
             self._warmup_left -= 1
             self.stream.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(self.stream):
+                if not self._ready:
+                    self._setup()
                 self._body()
                 self._zero_grad()
             torch.cuda.current_stream(self.device).wait_stream(self.stream)

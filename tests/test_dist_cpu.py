@@ -81,7 +81,7 @@ def _bucket_worker(rank, world, port, tmp, in_place):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
-    from residual_stream_burden_b200.dist import BucketedGradExchange, shard_batch
+    from residual_stream_burden_b200.dist import BucketedGradExchange, observe_ready_order, shard_batch
     try:
         torch.manual_seed(0)                                   # same model and full batch on every rank
         net = torch.nn.Sequential(torch.nn.Linear(12, 40), torch.nn.Tanh(), torch.nn.Linear(40, 40), torch.nn.Tanh(),
@@ -93,7 +93,18 @@ def _bucket_worker(rank, world, port, tmp, in_place):
         ex = BucketedGradExchange(params, bucket_bytes=500, in_place=in_place, small_numel=100,
                                   on_bucket_reduced=order.append)
         assert len(ex.buckets) >= 3
-        assert ex.buckets[0][0] is unused and ex.buckets[0][1] is net[4].bias          # backward order
+        assert ex.buckets[0][0] is unused and ex.buckets[0][1] is net[4].bias          # reverse registration order
+        # the order observed in a real backward pass: last layer first, the parameter without a gradient last
+        seen = observe_ready_order(params, lambda: (net(x) - y).square().mean().backward())
+        assert len(seen) == len(params) and {id(p) for p in seen} == {id(p) for p in params}
+        layer_of = {id(p): k for k in (0, 2, 4) for p in net[k].parameters()}
+        layers = [layer_of[id(p)] for p in seen[:-1]]
+        assert layers == sorted(layers, reverse=True) and seen[-1] is unused
+        for p in params:
+            p.grad = None
+        by_order = BucketedGradExchange(seen, bucket_bytes=500, ready_order=True)
+        assert by_order.buckets[0][0] is seen[0] and by_order.buckets[-1][-1] is unused
+        by_order.remove()
         for _ in range(2):                                     # two steps: the bookkeeping resets
             for p in params:
                 p.grad = None

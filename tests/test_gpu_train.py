@@ -104,9 +104,9 @@ def test_captured_step_exchange_hooks_with_a_single_rank_group(monkeypatch, tmp_
             # the graph captures collectives: it is closed before the group is destroyed, whatever happens
             with T.TrainStep(m, batch, compile_model=False, force_exchange=True, bucket_mb=0.05,
                              in_place_exchange=in_place, warmup=2) as trainer:
-                assert trainer.exchange.active and len(trainer.exchange.buckets) > 1
                 got = [float(trainer.step(images[k], labels)) for k in range(steps)]
                 assert trainer.graph is not None
+                assert trainer.exchange.active and len(trainer.exchange.buckets) > 1
             torch.testing.assert_close(torch.tensor(got), torch.tensor(want), atol=2e-3, rtol=2e-2)
             assert_same_training(m, ref, init)
     finally:

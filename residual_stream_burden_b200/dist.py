@@ -97,23 +97,29 @@ class BucketedGradExchange:
 
     def __init__(self, params: Sequence[torch.nn.Parameter], group=None, bucket_bytes: int = 256 << 20,
                  in_place: bool = True, small_numel: int = 1 << 16, comm_stream=None, force: bool = False,
-                 on_bucket_reduced=None, ready_order: bool = False):
+                 on_bucket_reduced=None, ready_order: bool = False, tail_buckets: bool = True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
         self.active = self.world > 1 or (force and dist.is_available() and dist.is_initialized())
         self.in_place, self.small_numel = in_place, small_numel
         self.on_bucket_reduced = on_bucket_reduced
         params = [p for p in params if p.requires_grad]
+        ordered = list(params if ready_order else reversed(params))      # the order the gradients become ready
+        # Buckets are cut from the END of that order: the last bucket's all-reduce (and update) cannot hide behind
+        # any backward work, so the last two buckets are kept small (1/16 and 1/4 of the regular size).
+        caps = [max(bucket_bytes // 16, 1), max(bucket_bytes // 4, 1)]
         self.buckets: list[list[torch.nn.Parameter]] = []
         current, size = [], 0
-        for p in (params if ready_order else reversed(params)):          # the order the gradients become ready
+        for p in reversed(ordered):
             current.append(p)
             size += p.numel() * p.element_size()
-            if size >= bucket_bytes:
-                self.buckets.append(current)
+            cap = caps[len(self.buckets)] if len(self.buckets) < len(caps) and tail_buckets else bucket_bytes
+            if size >= cap:
+                self.buckets.append(current[::-1])
                 current, size = [], 0
         if current:
-            self.buckets.append(current)
+            self.buckets.append(current[::-1])
+        self.buckets.reverse()
         self._bucket_of = {id(p): k for k, bucket in enumerate(self.buckets) for p in bucket}
         self._pending = [0] * len(self.buckets)
         self._launched = [False] * len(self.buckets)

@@ -85,6 +85,9 @@ def parse_args():
     ap.add_argument("--no-overlap-optimizer", dest="overlap_optimizer", action="store_false",
                     help="single-graph step: one AdamW update after backward instead of per-bucket updates on the side "
                          "stream right after each bucket's all-reduce")
+    ap.add_argument("--no-shard-optimizer", dest="shard_optimizer", action="store_false",
+                    help="single-graph step: every rank updates all parameters after an all-reduce instead of 1/N of them "
+                         "between a reduce-scatter and an all-gather")
     ap.add_argument("--sweep-slots", default="2,4,8", help="n values of --sweep")
     ap.add_argument("--sweep-channels", default="768,1152", help="widths of --sweep")
     ap.add_argument("--sweep-log2", default="12-20", help="range lo-hi of log2(tokens) of --sweep")
@@ -594,7 +597,7 @@ def time_device(fn, steps, warmup, world, device):
 
 
 def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_steps=50, compile_model=True,
-                   train_impl="graph", bucket_mb=256, overlap_optimizer=True, train_schedule="literal"):
+                   train_impl="graph", bucket_mb=256, overlap_optimizer=True, train_schedule="literal", shard_optimizer=True):
     """SiHC-B forward (batch 256), SiHC-XL training step (batch 32 per GPU, DDP) or SiHC-XL Heun sampling
     (batch 256 per GPU, CFG 2.4 on [0.1, 0.9]); bf16 autocast over fp32 parameters, synthetic N(0,1) images,
     random-init weights with opened gates.  Inputs start in pinned host memory every step.
@@ -642,7 +645,8 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
         model = sihc_xl().to(device)
         model.open_gates()
         trainer = TrainStep(model, batch, lr=2e-4, betas=(0.9, 0.95), weight_decay=0.0, compile_model=compile_model,
-                            bucket_mb=bucket_mb, overlap_optimizer=overlap_optimizer, schedule=train_schedule)
+                            bucket_mb=bucket_mb, overlap_optimizer=overlap_optimizer, schedule=train_schedule,
+                            shard_optimizer=shard_optimizer)
         x_host = torch.randn(batch, 3, 256, 256, generator=gen).pin_memory()
         y = torch.randint(0, 1000, (batch,), device=device)
         trainer.step(x_host, y)                     # first eager pass: compiles the sublayers
@@ -664,7 +668,9 @@ def model_workload(kind, device, rank, world, local_rank, steps, warmup, sample_
                 "one CUDA graph per step (%s, gradient all-reduce in %d MB buckets under backward%s)"
                 % ("factored stages with the stage-scoped backward" if train_schedule == "stage"
                    else "literal schedule: fused write+read step and its fused adjoint",
-                   bucket_mb, ", per-bucket AdamW on the side stream" if overlap_optimizer else ""))
+                   bucket_mb, (", per-bucket AdamW on the side stream" + (" on this rank's 1/N of every parameter "
+                               "(reduce-scatter, update, all-gather)" if shard_optimizer and world > 1 else ""))
+                   if overlap_optimizer else ""))
     elif kind == "sihc_xl_train":
         batch = 32
         model = sihc_xl().to(device)
@@ -845,7 +851,7 @@ def main():
         warm = max(args.warmup, 1) if args.workload == "sihc_xl_sample" else max(args.warmup, 3)
         res = model_workload(args.workload, device, rank, world, local_rank, args.steps, warm,
                              args.sample_steps, not args.no_compile, args.train_impl, args.bucket_mb,
-                             args.overlap_optimizer, args.train_schedule)
+                             args.overlap_optimizer, args.train_schedule, args.shard_optimizer)
         clocks = sampler.stop() if rank == 0 else None
         if rank == 0:
             print(json.dumps({"metric": args.workload + "_throughput", "value": res["img_per_s"], "unit": "img/s",
@@ -982,7 +988,7 @@ def main():
             try:
                 models[kind] = model_workload(kind, device, rank, world, local_rank, 20, 8, 50, cm,
                                               args.train_impl, args.bucket_mb, args.overlap_optimizer,
-                                              args.train_schedule)
+                                              args.train_schedule, args.shard_optimizer)
             except Exception as exc:                               # noqa: BLE001
                 if world > 1:
                     raise                                          # see above: never leave the peers waiting

@@ -192,3 +192,78 @@ class BucketedGradExchange:
                 torch._foreach_copy_(small, [v.view_as(g) for v, g in zip(flat.split([g.numel() for g in small]), small)])
         if self.on_bucket_reduced is not None:
             self.on_bucket_reduced(k)
+
+
+class ShardedGradExchange(BucketedGradExchange):
+    """:class:`BucketedGradExchange` with the update sharded over the ranks (optimizer-state sharding).
+
+    For every large gradient tensor of a bucket the all-reduce is replaced by its two halves with the update in
+    between: reduce-scatter (in place: rank r ends up with the mean of slice r), the optimizer step on that slice only
+    (``on_bucket_reduced``), all-gather of the updated parameter slices (in place).  The bytes crossing NVLink are those
+    of the all-reduce, but each rank runs the optimizer - a pass over four fp32 arrays per parameter, bound by device
+    memory bandwidth and competing with the backward pass for it - on 1/N of the elements, and keeps 1/N of the
+    optimizer state.  No flat copies: gradients and parameters are reduced and gathered where they lie.  Tensors that
+    are small, not contiguous or not divisible by the number of ranks keep the all-reduce and are updated in full on
+    every rank.  With a single rank the slices are the whole tensors and no collective runs.
+
+    ``update_tensors(k)`` gives, for bucket k, the tensors the caller's optimizer must own (parameter slices and whole
+    small parameters); :meth:`attach_grads` points their ``.grad`` at this step's gradients before the optimizer runs.
+    """
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.rank = dist.get_rank(self.group) if self.world > 1 else 0
+        backend = dist.get_backend(self.group) if self.active else None
+        self._native_scatter = backend == "nccl"          # gloo has no reduce-scatter: all-reduce and keep the slice
+        self._sharded, self._whole, self._slices = [], [], []
+        for bucket in self.buckets:
+            sharded = [p for p in bucket if p.numel() >= self.small_numel and p.numel() % self.world == 0
+                       and p.data.is_contiguous()]
+            ids = {id(p) for p in sharded}
+            self._sharded.append(sharded)
+            self._whole.append([p for p in bucket if id(p) not in ids])
+            n = [p.numel() // self.world for p in sharded]
+            self._slices.append([p.data.view(-1)[self.rank * m:(self.rank + 1) * m] for p, m in zip(sharded, n)])
+
+    def update_tensors(self, k: int) -> list:
+        return list(self._slices[k]) + list(self._whole[k])
+
+    def attach_grads(self, k: int) -> None:
+        for p, piece in zip(self._sharded[k], self._slices[k]):
+            m = piece.numel()
+            piece.grad = None if p.grad is None else p.grad.view(-1)[self.rank * m:(self.rank + 1) * m]
+
+    def _reduce_on_current_stream(self, k: int, grads) -> None:
+        sharded = [p for p in self._sharded[k] if p.grad is not None]
+        for p in sharded:
+            if not p.grad.is_contiguous():
+                p.grad = p.grad.contiguous()
+        whole = [p.grad for p in self._whole[k] if p.grad is not None]
+        if self.active:
+            flats = [p.grad.view(-1) for p in sharded]
+            if self._native_scatter and flats:
+                with dist._coalescing_manager(group=self.group):
+                    for g in flats:
+                        m = g.numel() // self.world
+                        dist.reduce_scatter_tensor(g[self.rank * m:(self.rank + 1) * m], g, op=self._avg_op, group=self.group)
+            elif flats:
+                with dist._coalescing_manager(group=self.group):
+                    for g in flats:
+                        dist.all_reduce(g, op=self._avg_op, group=self.group)
+                if self._divide:
+                    torch._foreach_div_(flats, float(self.world))
+            if whole:
+                flat = torch.cat([g.reshape(-1) for g in whole])
+                dist.all_reduce(flat, op=self._avg_op, group=self.group)
+                if self._divide:
+                    flat /= float(self.world)
+                torch._foreach_copy_(whole, [v.view_as(g) for v, g in zip(flat.split([g.numel() for g in whole]), whole)])
+        self.attach_grads(k)
+        if self.on_bucket_reduced is not None:
+            self.on_bucket_reduced(k)
+        if self.active and sharded:
+            with dist._coalescing_manager(group=self.group):
+                for p in sharded:
+                    d = p.data.view(-1)
+                    m = d.numel() // self.world
+                    dist.all_gather_into_tensor(d, d[self.rank * m:(self.rank + 1) * m], group=self.group)

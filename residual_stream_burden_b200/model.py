@@ -346,14 +346,25 @@ class SiHC(nn.Module):
         """The connection events of a stage, in order: ``(connection, update, uses_context)`` where
         ``update(seq, rope)`` is the gated sublayer (or whole-block) update of a token sequence."""
         events = []
+        mods: dict = {}
+
+        def modulation(block):
+            # Computed when the block's first event runs (as the reference's loop does, sihc/models/sihc/sublayer.py:63),
+            # not when the event list is built: autograd runs backward nodes in reverse creation order, so a modulation
+            # created up front would get its gradient - and its 6C x C weight gradient - only at the very end of the
+            # stage's (or, in the literal schedule, the model's) backward, where nothing is left to overlap its
+            # all-reduce with.
+            if id(block) not in mods:
+                mods[id(block)] = block.branch.conditioning(cond)
+            return mods[id(block)]
+
         for i, block in enumerate(blocks):
             ctx = bool(self.in_context_len) and stage_start + i >= self.in_context_start
             if self.frequency == "sublayer":
-                mod = block.branch.conditioning(cond)
                 events.append((block.attention_connection,
-                               lambda seq, rope, b=block, m=mod: b.branch.attention_update(seq, m, rope), ctx))
+                               lambda seq, rope, b=block: b.branch.attention_update(seq, modulation(b), rope), ctx))
                 events.append((block.mlp_connection,
-                               lambda seq, rope, b=block, m=mod: b.branch.mlp_update(seq, m), ctx))
+                               lambda seq, rope, b=block: b.branch.mlp_update(seq, modulation(b)), ctx))
             else:
                 events.append((block.connection, lambda seq, rope, b=block: b.branch(seq, cond, rope), ctx))
         return events

@@ -31,7 +31,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
-from .dist import BucketedGradExchange, observe_ready_order
+from .dist import BucketedGradExchange, ShardedGradExchange, observe_ready_order
 from .model import Branch, SiHC, velocity_training_batch
 
 
@@ -72,12 +72,14 @@ class TrainStep:
     one update after backward.  ``use_graph=False`` runs the same step eagerly (for tests and debugging).
     ``schedule``: ``"stage"`` = the reference's factored stages with the stage-scoped backward; ``"literal"`` = the
     literal recurrence with the fused write+read step and its fused adjoint (fewer bytes when n <= 4).
+    ``shard_optimizer`` (with ``overlap_optimizer``): each rank updates 1/N of every large parameter between a
+    reduce-scatter of its gradient and an all-gather of the result (:class:`.dist.ShardedGradExchange`).
     """
 
     def __init__(self, model: SiHC, batch: int, *, lr: float = 2e-4, betas=(0.9, 0.95), weight_decay: float = 0.0,
                  group=None, bucket_mb: float = 256, in_place_exchange: bool = True, overlap_optimizer: bool = False,
                  compile_model: bool = True, use_graph: bool = True, force_exchange: bool = False, warmup: int = 3,
-                 schedule: str = "stage"):
+                 schedule: str = "stage", shard_optimizer: bool = True):
         device = next(model.parameters()).device
         if device.type != "cuda":
             raise ValueError("TrainStep needs the model on a CUDA device")
@@ -98,6 +100,7 @@ class TrainStep:
                                  force=force_exchange)
         self._opt_kw = dict(lr=lr, betas=betas, weight_decay=weight_decay, fused=True, capturable=use_graph)
         self._overlap_optimizer = overlap_optimizer
+        self._shard_optimizer = shard_optimizer
         self.exchange: Optional[BucketedGradExchange] = None
         self.bucket_optimizers = None
         self.optimizer = None
@@ -120,13 +123,19 @@ class TrainStep:
         order = observe_ready_order(params, probe)
         self._zero_grad()
         distributed = dist.is_available() and dist.is_initialized()
-        if distributed or self._overlap_optimizer:
+        if self._overlap_optimizer and self._shard_optimizer:
+            # reduce-scatter -> update of this rank's slices -> all-gather, bucket by bucket on the side stream
+            self.exchange = ShardedGradExchange(order, ready_order=True, on_bucket_reduced=self._bucket_ready,
+                                                **self._exchange_kw)
+            self.bucket_optimizers = [torch.optim.AdamW(self.exchange.update_tensors(k), **self._opt_kw)
+                                      for k in range(len(self.exchange.buckets))]
+        elif distributed or self._overlap_optimizer:
             self.exchange = BucketedGradExchange(order, ready_order=True,
                                                  on_bucket_reduced=self._bucket_ready if self._overlap_optimizer else None,
                                                  **self._exchange_kw)
-        if self._overlap_optimizer:
-            self.bucket_optimizers = [torch.optim.AdamW(bucket, **self._opt_kw) for bucket in self.exchange.buckets]
-        else:
+            if self._overlap_optimizer:
+                self.bucket_optimizers = [torch.optim.AdamW(bucket, **self._opt_kw) for bucket in self.exchange.buckets]
+        if not self._overlap_optimizer:
             self.optimizer = torch.optim.AdamW(params, **self._opt_kw)
         self._ready = True
 
@@ -150,6 +159,10 @@ class TrainStep:
     def _zero_grad(self) -> None:
         for p in self.model.parameters():
             p.grad = None
+        if isinstance(self.exchange, ShardedGradExchange):
+            for k in range(len(self.exchange.buckets)):
+                for piece in self.exchange._slices[k]:
+                    piece.grad = None
 
     def _capture(self) -> None:
         self._zero_grad()                          # backward allocates the gradients inside the graph's pool

@@ -141,3 +141,61 @@ def test_bucketed_exchange_averages_gradients_during_backward(tmp_path, in_place
     errs = [p.read_text() for p in tmp_path.iterdir() if p.name.startswith("err")]
     assert not errs, errs[0]
     assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
+
+
+def _sharded_worker(rank, world, port, tmp):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+    from residual_stream_burden_b200.dist import ShardedGradExchange, observe_ready_order, shard_batch
+    try:
+        torch.manual_seed(0)
+        def make():
+            torch.manual_seed(1)
+            return torch.nn.Sequential(torch.nn.Linear(12, 40), torch.nn.Tanh(), torch.nn.Linear(40, 41), torch.nn.Tanh(),
+                                       torch.nn.Linear(41, 3))
+        net, ref = make(), make()
+        x, y = torch.randn(8, 12), torch.randn(8, 3)
+        params = list(net.parameters())
+        order = observe_ready_order(params, lambda: (net(x) - y).square().mean().backward())
+        for p in params:
+            p.grad = None
+        opts = []
+        ex = ShardedGradExchange(order, ready_order=True, bucket_bytes=2000, small_numel=100,
+                                 on_bucket_reduced=lambda k: opts[k].step())
+        opts.extend(torch.optim.AdamW(ex.update_tensors(k), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.0)
+                    for k in range(len(ex.buckets)))
+        # 12x40 and 40x41 weights are sharded (even element counts), the 41x3 weight (123 elements) and biases are not
+        assert sum(len(s) for s in ex._sharded) == 2 and sum(len(s) for s in ex._whole) == 4
+        ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.0)
+        lo, hi = shard_batch(8, rank, world)
+        for _ in range(3):
+            for p in params:
+                p.grad = None
+            ex.begin()
+            (net(x[lo:hi]) - y[lo:hi]).square().mean().backward()
+            ex.finish()
+            ref_opt.zero_grad(set_to_none=True)
+            (ref(x) - y).square().mean().backward()            # full batch = mean over the two shards
+            ref_opt.step()
+        for a, b in zip(net.parameters(), ref.parameters()):
+            torch.testing.assert_close(a, b, atol=1e-6, rtol=1e-5)
+        ex.remove()
+        open(os.path.join(tmp, f"ok{rank}"), "w").write("ok")
+    except Exception:                                          # noqa: BLE001
+        import traceback
+        open(os.path.join(tmp, f"err{rank}"), "w").write(traceback.format_exc())
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:                                      # noqa: BLE001
+            pass
+
+
+def test_sharded_update_equals_full_batch_adamw(tmp_path):
+    """Reduce-scatter, update of each rank's slices, all-gather: after three steps both ranks hold the parameters a
+    single process gets from AdamW on the full batch."""
+    mp.spawn(_sharded_worker, args=(2, _port(), str(tmp_path)), nprocs=2, join=True)
+    errs = [p.read_text() for p in tmp_path.iterdir() if p.name.startswith("err")]
+    assert not errs, errs[0]
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()

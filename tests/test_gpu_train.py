@@ -51,10 +51,10 @@ def eager_reference(model, images, labels, steps, schedule="stage"):
     return losses
 
 
-@pytest.mark.parametrize("schedule,overlap_optimizer,compile_model", [("stage", False, False), ("stage", True, False),
-                                                                      ("stage", False, True), ("stage", True, True),
-                                                                      ("literal", True, False), ("literal", True, True)])
-def test_captured_step_matches_eager_training_loop(monkeypatch, schedule, compile_model, overlap_optimizer):
+@pytest.mark.parametrize("schedule,overlap_optimizer,compile_model,shard", [
+    ("stage", False, False, False), ("stage", True, False, False), ("stage", False, True, False), ("stage", True, True, True),
+    ("literal", True, False, True), ("literal", True, True, True)])
+def test_captured_step_matches_eager_training_loop(monkeypatch, schedule, compile_model, overlap_optimizer, shard):
     import residual_stream_burden_b200.train as T
     from residual_stream_burden_b200.model import SublayerSiHC
     monkeypatch.setattr(T, "velocity_training_batch", fixed_noise_batch)
@@ -69,7 +69,7 @@ def test_captured_step_matches_eager_training_loop(monkeypatch, schedule, compil
     want = eager_reference(ref, images, labels, steps, schedule)
 
     with T.TrainStep(model, batch, compile_model=compile_model, overlap_optimizer=overlap_optimizer,
-                     bucket_mb=0.05, warmup=2, schedule=schedule) as trainer:
+                     bucket_mb=0.05, warmup=2, schedule=schedule, shard_optimizer=shard) as trainer:
         got = [float(trainer.step(images[k], labels)) for k in range(steps)]
         assert trainer.graph is not None                          # steps 3.. ran as graph replays
         if overlap_optimizer:
@@ -99,11 +99,12 @@ def test_captured_step_exchange_hooks_with_a_single_rank_group(monkeypatch, tmp_
         images = [torch.randn(batch, 3, 256, 256, device="cuda") for _ in range(steps)]
         labels = torch.tensor([1, 2], device="cuda")
         want = eager_reference(ref, images, labels, steps)
-        for in_place in (True, False):
+        for in_place, sharded in ((True, False), (False, False), (True, True)):
             m = copy.deepcopy(model)
             # the graph captures collectives: it is closed before the group is destroyed, whatever happens
             with T.TrainStep(m, batch, compile_model=False, force_exchange=True, bucket_mb=0.05,
-                             in_place_exchange=in_place, warmup=2) as trainer:
+                             in_place_exchange=in_place, warmup=2, overlap_optimizer=sharded,
+                             shard_optimizer=sharded) as trainer:
                 got = [float(trainer.step(images[k], labels)) for k in range(steps)]
                 assert trainer.graph is not None
                 assert trainer.exchange.active and len(trainer.exchange.buckets) > 1

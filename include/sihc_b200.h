@@ -234,10 +234,12 @@ int sihc_tri_dgamma(const void* const* g, const void* const* dz, float* dgamma, 
  *   "threads", "tokens_per_thread", "blocks_per_sm", "partial_blocks_per_sm",
  *   "max_vector_bytes", "min_block_tokens", "stage_budget_kb" (KB of shared memory
  *   for a block's coefficient slice), "tri_chunk" (events per grid slice of the
- *   triangular backward, 1..8): value <= 0 restores the default.
+ *   triangular backward, 1..8), "token_lanes" (fewest token lanes per block of the fused literal
+ *   adjoint): value <= 0 restores the default.
  *   "ring_stages" (0 = register-staged single-event adjoints, 3..8 = async-copy ring),
  *   "stage_smem" (0 = stage coefficients from L1, 1 = from shared memory),
- *   "wgrad_tiled" (0 = per-thread, 1 = block-tiled stage weight gradient): a negative
+ *   "wgrad_tiled" (0 = per-thread, 1 = block-tiled stage weight gradient),
+ *   "half_vectors" (fused literal adjoint: 1 = half-width vectors and twice the channel lanes): a negative
  *   value restores the per-kernel default ("ring_default" / "stage_smem_default"
  *   with any value do the same).
  * Returns 0, or SIHC_ERR_NULL for an unknown name.  (Counterpart of the

@@ -99,11 +99,19 @@ inline cudaError_t launch_persistent(K kernel, P& params, const Problem& pb, int
 template <typename K, typename P>
 inline cudaError_t launch_persistent_smem(K kernel, P& params, const Problem& pb, int V, int default_threads,
                                           size_t smem_per_thread, bool emits_partials, uint32_t* gx_out,
-                                          int max_threads = kMaxThreads) {
+                                          int max_threads = kMaxThreads, uint32_t min_token_lanes = 1) {
     constexpr size_t kMaxDynamic = 200 * 1024;     // leaves room for the static reduction buffer
     const Tuning& tn = tuning();
     const uint32_t ncv = pb.C / static_cast<uint32_t>(V);
     BlockShape bs = block_shape(ncv, tn.threads > 0 ? tn.threads : default_threads, max_threads);
+    // A kernel whose speed comes from token-level parallelism (many warps each walking its own tokens) can ask for a
+    // minimum number of token lanes: the channel vectors are then split evenly over blockIdx.y until they fit.
+    for (uint32_t parts = 2; bs.tl < min_token_lanes && parts <= 8 && ncv / parts >= 16; ++parts) {
+        if (ncv % parts != 0) continue;
+        BlockShape alt = block_shape(ncv / parts, tn.threads > 0 ? tn.threads : default_threads, max_threads);
+        alt.gy = parts;
+        if (alt.tl > bs.tl) bs = alt;
+    }
     while (bs.tl > 1 && static_cast<size_t>(bs.threads) * smem_per_thread > kMaxDynamic) { --bs.tl; bs.threads = bs.cl * bs.tl; }
     const size_t smem = static_cast<size_t>(bs.threads) * smem_per_thread;
     if (smem > kMaxDynamic) return cudaErrorInvalidConfiguration;

@@ -140,8 +140,14 @@ __global__ void __launch_bounds__(kLiteralBwdThreads) write_read_bwd_kernel(cons
 // (NST stages, private slots, no block barrier - the scheme of the single-event adjoints in sihc_ring.cu).  The
 // register-staged kernel above holds 2*S*V accumulators and 2*S*V coefficients and has no registers left to keep a
 // second token's loads in flight; here the loads never occupy registers while they travel.  Vector path only.
-constexpr int kLiteralRingThreads = 256;       // target; whole channel rows round it to at most kLiteralRingMaxThreads
-constexpr int kLiteralRingMaxThreads = 320;
+// Block shape of the ring form.  Its speed comes from token-level parallelism - many warps, each walking its own tokens
+// through ~500 dependent instructions per token - so the channel vectors are split over blockIdx.y until a block of
+// about 256 threads has at least 4 (width <= 768) or 6 token lanes.  Measured on B200, bf16, GB/s of the 3S+3 elements:
+// 65 536 tokens x 768: 3 lanes x 96 channel lanes 4475, 4 x 96 (384 threads) 4750, 5 x 48 5185; 8192 x 768: 3934;
+// 8192 x 1152: 2 x 144 3485, 7 x 36 4045; 65 536 x 1152: 4600-4750.  Half-width vectors (twice the channel lanes, same
+// token lanes) gain 3 % over 3 x 96 and lose against more token lanes.
+constexpr int kLiteralRingThreads = 256;       // target; whole channel slices round it to at most kLiteralRingMaxThreads
+constexpr int kLiteralRingMaxThreads = 384;
 constexpr int kLiteralRingStages = 3;
 // Half-width form: V/2 channels per thread, twice the threads (and warps) for the same bytes in flight.
 constexpr int kLiteralHalfThreads = 512;
@@ -291,7 +297,7 @@ cudaError_t launch_write_read_bwd(const Problem& pb, const void* h, const void* 
             const int ring = tuning().ring;       // 0 = register-staged form, otherwise the ring (default)
             if constexpr (VM * int(sizeof(T)) >= 4) {
                 constexpr int VH = (S * VM >= 32 && VM * int(sizeof(T)) >= 8) ? VM / 2 : VM;
-                if (ring != 0 && tuning().half_vectors != 0 && VH != VM) {
+                if (ring != 0 && tuning().half_vectors > 0 && VH != VM) {
                     return launch_persistent_smem(write_read_bwd_ring_kernel<T, W, S, VH, kLiteralRingStages, kLiteralHalfMaxThreads>,
                                                   p, pb, VH, kLiteralHalfThreads,
                                                   static_cast<size_t>(kLiteralRingStages) * (2 * S + 2) * VH * sizeof(T),
@@ -306,7 +312,8 @@ cudaError_t launch_write_read_bwd(const Problem& pb, const void* h, const void* 
                     return launch_persistent_smem(write_read_bwd_ring_kernel<T, W, S, VM, kLiteralRingStages, kLiteralRingMaxThreads>,
                                                   p, pb, VM, kLiteralRingThreads,
                                                   static_cast<size_t>(kLiteralRingStages) * (2 * S + 2) * VM * sizeof(T),
-                                                  partial != nullptr, blocks, kLiteralRingMaxThreads);
+                                                  partial != nullptr, blocks, kLiteralRingMaxThreads,
+                                                  static_cast<uint32_t>(tuning().token_lanes > 0 ? tuning().token_lanes : (pb.C / VM <= 96 ? 4 : 6)));
                 }
             }
             return launch_persistent(write_read_bwd_kernel<T, W, S, VM>, p, pb, VM, 1, kLiteralBwdThreads, 1,

@@ -247,15 +247,21 @@ cudaError_t launch_tri_dgamma(const Problem& pb, const void* const* g, const voi
             // six or more 4x4 blocks of the matrix.  Measured on B200, bf16, GB/s of the 2(E-1) tensors read:
             // 24 events, 65 536 tokens x 768: 2058 -> 2391; 8192 x 1152: 2001 -> 2308; 16 events 2569 -> 2906;
             // 12 events 3660 -> 4086; but 8 events (three 4x4 blocks, 192 threads) 4345 -> 3083.
-            // The `tokens_per_thread` knob forces one shape (4 or 8).
+            // The `tokens_per_thread` knob forces a shape: 4 = (4 tokens, 3 stages), 8 = (8, 2), 12 = (8, 3), 16 = (16, 2).
             const int forced = tuning().tt;
-            const bool wide = forced == 8 || (forced != kTriGammaTokens && s.nblk >= 6);
-            if (wide && s.smem * 4 / 3 <= kTriGammaMaxSmem) {
-                kernel = tri_dgamma_kernel<T, 2 * kTriGammaTokens, kTriGammaStages - 1>;
-                t.ntiles = (pb.M + 2 * kTriGammaTokens - 1) / (2 * kTriGammaTokens);
-                smem = s.smem * 4 / 3;
+            const bool wide = forced == 8 || (forced != kTriGammaTokens && forced != 12 && forced != 16 && s.nblk >= 6);
+            auto use = [&](auto k, int tokens, int stages) {
+                const size_t need = s.smem * static_cast<size_t>(tokens * stages) / (kTriGammaTokens * kTriGammaStages);
+                if (need > kTriGammaMaxSmem) return false;
+                kernel = k;
+                t.ntiles = (pb.M + tokens - 1) / tokens;
+                smem = need;
                 if (gx > t.ntiles) gx = t.ntiles;
-            }
+                return true;
+            };
+            if (forced == 12) use(tri_dgamma_kernel<T, 8, 3>, 8, 3);
+            else if (forced == 16) use(tri_dgamma_kernel<T, 16, 2>, 16, 2);
+            else if (wide) use(tri_dgamma_kernel<T, 2 * kTriGammaTokens, kTriGammaStages - 1>, 8, 2);
             if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kTriGammaMaxSmem)) return e;
             kernel<<<dim3(gx, s.gy, 1), s.threads, smem, pb.stream>>>(p);
             count_launch();

@@ -424,9 +424,12 @@ def run_sweep(args, device, rank, world):
 # ------------------------------------------------------------------------------------------ stage ops
 def run_stage_ops(args, device, steps, warmup):
     """The multi-event stage operators one by one on SiHC-B's stage shapes (the SiHC-B forward configuration: batch 256,
-    256 tokens, n=4, width 768, E=24 events): read(E), triangular(E-1), write(E) and their backward calls.
-    GB/s are algorithmic bytes (read S+E, write 2S+E, triangular J+2, read bwd 2(S+E) as two kernels,
-    write bwd 2(S+E), triangular bwd 2J+1) over the CUDA-event time of the C ABI call."""
+    256 tokens, n=4, width 768, E=24 events): read(E), triangular(E-1), write(E) and their backward calls, plus the
+    literal schedule's fused step and its fused adjoint, the one-pass stage coefficient gradient and the device's
+    write-only bandwidth.  GB/s are algorithmic bytes (read S+E, write 2S+E, triangular J+2, read bwd 2(S+E) as two
+    kernels, write bwd 2(S+E), triangular bwd 2J+1, literal step 2S+2, its adjoint 3S+3, stage dgamma 2(E-1)) over the
+    CUDA-event time of the C ABI call; `value` is the six factored-stage operators as a set.  The reference's own
+    Triton operators are timed on the same tensors as a labelled comparator."""
     from residual_stream_burden_b200 import _lib
     lib = _lib.lib
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32

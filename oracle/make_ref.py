@@ -22,7 +22,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
-DEFAULT_SOURCE = "/root/reference"
+DEFAULT_SOURCE = os.environ.get("SIHC_REFERENCE_ROOT", "/root/reference")      # the read-only reference checkout
 
 
 def make_ref(source: str = DEFAULT_SOURCE) -> str | None:

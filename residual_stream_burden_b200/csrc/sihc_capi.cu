@@ -338,6 +338,9 @@ int sihc_read_bwd(const void* x, const void* const* g, const void* alpha, void* 
         e = launch_read_bwd1_ring(pb, x, g[0], alpha, dx, partial, &blocks, ring, kReadBwdRingThreads);
     } else if (events == 1) {
         e = launch_read_bwd1(pb, x, g[0], alpha, dx, partial, &blocks);
+    } else if (dx && dalpha && read_bwd_tiled_applies(pb)) {
+        // both adjoints from one pass over x and the gradients: 2S + E elements ("stage_smem" = 0 restores two kernels)
+        e = launch_read_bwd_tiled(pb, x, g, alpha, dx, partial, &blocks);
     } else {
         e = cudaSuccess;
         if (dx) e = launch_write_fwd(pb, nullptr, g, alpha, dx);
@@ -379,6 +382,9 @@ int sihc_write_bwd(const void* h, const void* const* dz, const void* beta, void*
                                    kWriteBwdRingThreads);
     } else if (events == 1) {
         e = launch_write_bwd1(pb, h, dbeta ? dz[0] : nullptr, beta, want_ddz ? ddz[0] : nullptr, partial, &blocks);
+    } else if (want_ddz && dbeta && wgrad_tiled_read_applies(pb) && tuning().stage_smem != 0) {
+        // both adjoints from one pass over h: S + 2E elements (the "stage_smem" = 0 knob restores the two-kernel form)
+        e = launch_wgrad_tiled_read(pb, h, dz, beta, ddz, partial, &blocks);
     } else {
         e = cudaSuccess;
         if (want_ddz) e = launch_read_fwd(pb, h, beta, ddz);

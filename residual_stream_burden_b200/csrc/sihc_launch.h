@@ -70,6 +70,8 @@ struct ReadBwd1Params { const void* x; const void* g; const void* w; void* dx; f
 struct WriteBwd1Params { const void* h; const void* dz; const void* w; void* ddz; float* partial; Tiling t; };
 // Multi-event weight gradient partials: [P][E][S][C].
 struct WGradParams { const void* x; ConstPtrs z; float* partial; int E; Tiling t; };
+// The tiled weight gradient with the write's other adjoint in the same pass: ddz[l][m,c] = sum_s w[l,c,s] * x[m,s,c].
+struct WGradReadParams { const void* x; ConstPtrs z; float* partial; int E; Tiling t; const void* w; MutPtrs out; };
 // Events handled per pass over the carrier by the stage weight-gradient kernel.
 template <int S, int V> struct EventChunk {
     static constexpr int raw = 64 / (S * V);
@@ -79,6 +81,12 @@ template <int S, int V> struct EventChunk {
 // the threads that own different events (sihc_wgrad.cu).  Vector path only.
 cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const void* const* z, float* partial,
                                uint32_t* blocks);
+// Whether the one-pass form below serves this problem (vector path, 4 slots, >= 16 events, weights in the tensor dtype).
+bool wgrad_tiled_read_applies(const Problem& pb);
+// One pass over the carrier gradient for BOTH adjoints of the stage write: the dbeta partials of launch_wgrad_tiled and
+// ddz[l] = sum_s beta[l,c,s] * h[m,s,c] (null ddz[l] skipped): S + 2E elements instead of 2(S + E).
+cudaError_t launch_wgrad_tiled_read(const Problem& pb, const void* carrier, const void* const* z, const void* beta,
+                                    void* const* ddz, float* partial, uint32_t* blocks);
 cudaError_t launch_wgrad(const Problem& pb, const void* carrier, const void* const* z, float* partial,
                          uint32_t* blocks);
 // out[(row / S) * C * S + c * S + row % S] = sum_p partial[(p * rows + row) * C + c]
@@ -93,6 +101,12 @@ cudaError_t launch_tri_bwd(const Problem& pb, const void* grad, const void* cons
 cudaError_t launch_write_read_bwd(const Problem& pb, const void* h, const void* gz, const void* y, const void* dz,
                                   const void* beta, const void* alpha_next, void* hh, void* ddz, float* partial,
                                   uint32_t* blocks);
+
+// One pass over the carrier and the E gradients for BOTH adjoints of the stage read (4 slots, 16..24 events, weights in
+// the tensor dtype): dx = sum_l alpha_l * g_l and the dalpha partials: 2S + E elements instead of 2(S + E).
+bool read_bwd_tiled_applies(const Problem& pb);
+cudaError_t launch_read_bwd_tiled(const Problem& pb, const void* carrier, const void* const* g, const void* alpha, void* dx,
+                                  float* partial, uint32_t* blocks);
 
 // Whole-stage coefficient gradient dgamma[i][j][c] = sum_m g_i * dz_j (j < i; zero elsewhere), [E][E][C] fp32, from one
 // pass over the E-1 recorded gradients and E-1 updates (sihc_trigamma.cu).  Needs C * element size % 16 == 0 and

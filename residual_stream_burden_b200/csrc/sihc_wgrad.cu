@@ -18,8 +18,8 @@ constexpr int kWGradTileDefaultThreads = 192; // default target: two blocks per 
 constexpr int kWGradTileTokens = 4;      // tokens per stage and stages of the tile ring, unless dispatch_tile_shape
 constexpr int kWGradTileStages = 3;      // picks the (8, 2) shape
 
-template <typename T, int S, int V, int TK, int NST>
-__global__ void __launch_bounds__(kWGradTileThreads) wgrad_tiled_kernel(const __grid_constant__ WGradParams p) {
+template <typename T, int S, int V, int TK, int NST, bool READ = false, typename P = WGradParams>
+__global__ void __launch_bounds__(READ ? kWGradTileDefaultThreads : kWGradTileThreads) wgrad_tiled_kernel(const __grid_constant__ P p) {
     constexpr int EC = EventChunk<S, V>::value;
     typedef VecIO<T, V> IO;
     typedef typename IO::Raw Raw;
@@ -68,6 +68,27 @@ __global__ void __launch_bounds__(kWGradTileThreads) wgrad_tiled_kernel(const __
 #pragma unroll
         for (int v = 0; v < V; ++v) acc[a][v] = 0.f;
 
+    // READ: this thread also produces ddz for its EC events, from the same carrier tile: packed coefficients
+    // w[l][c0..c0+V)[s] stay in registers (EC*S vectors), one output vector per event and token.
+    Raw wr[READ ? EC * S : 1];
+    T* outp[READ ? EC : 1];
+    if constexpr (READ) {
+#pragma unroll
+        for (int j = 0; j < EC; ++j) {
+            const int l = e0 + j;
+            const bool live = ln.active && l < p.E;
+            outp[j] = live && p.out.p[l] != nullptr ? static_cast<T*>(p.out.p[l]) + ln.c0 : nullptr;
+            float f[S][V];
+#pragma unroll
+            for (int s = 0; s < S; ++s)
+#pragma unroll
+                for (int v = 0; v < V; ++v) f[s][v] = 0.f;
+            if (live) load_coeffs<T, S, V>(static_cast<const T*>(p.w) + (static_cast<size_t>(l) * t.C + ln.c0) * S, f);
+#pragma unroll
+            for (int s = 0; s < S; ++s) wr[j * S + s] = IO::pack(f[s]);        // exact: the values are storage values
+        }
+    }
+
     uint32_t tile = blockIdx.x;
 #pragma unroll
     for (int st = 0; st < NST - 1; ++st) issue(tile + st * gridDim.x, st);
@@ -83,11 +104,29 @@ __global__ void __launch_bounds__(kWGradTileThreads) wgrad_tiled_kernel(const __
             Raw zr[EC];
 #pragma unroll
             for (int j = 0; j < EC; ++j) zr[j] = zt[static_cast<size_t>(tok * EC + j) * nthreads];
+            float rd[READ ? EC : 1][V];
+            if constexpr (READ) {
+#pragma unroll
+                for (int j = 0; j < EC; ++j)
+#pragma unroll
+                    for (int v = 0; v < V; ++v) rd[j][v] = 0.f;
+            }
 #pragma unroll
             for (int s = 0; s < S; ++s) {
                 const Raw xr = xt[static_cast<size_t>(tok * S + s) * CL];
 #pragma unroll
-                for (int j = 0; j < EC; ++j) IO::fma_raw(xr, zr[j], acc[j * S + s]);
+                for (int j = 0; j < EC; ++j) {
+                    IO::fma_raw(xr, zr[j], acc[j * S + s]);
+                    if constexpr (READ) IO::fma_raw(wr[j * S + s], xr, rd[j]);
+                }
+            }
+            if constexpr (READ) {
+                const uint32_t m = tile * TK + tok;
+                if (m < t.M) {
+#pragma unroll
+                    for (int j = 0; j < EC; ++j)
+                        if (outp[j] != nullptr) IO::store(outp[j] + static_cast<size_t>(m) * t.C, rd[j]);
+                }
             }
         }
         stage = stage + 1 == NST ? 0 : stage + 1;
@@ -108,6 +147,153 @@ __global__ void __launch_bounds__(kWGradTileThreads) wgrad_tiled_kernel(const __
     }
 }
 
+constexpr uint32_t kReadBwdTileLanes = 16;
+constexpr uint32_t kReadBwdTileRowStride = 18;
+
+// ---- one-pass stage read backward (4 slots) ---------------------------------------------------------------------------
+//   dx[m,s,c]          = sum_l alpha[l,c,s] * g_l[m,c]
+//   partial[b][l][s][c] = sum_{m in block b} X[m,s,c] * g_l[m,c]
+// from ONE pass over X and the E gradients (2S + E elements per token and channel; the two-kernel form - the write kernel
+// without carry for dx, then the weight gradient - reads the gradients twice: 2(S + E)).  The reference makes the same two
+// passes (`_write_impl(..., add_x=False)` and `_weights_backward`, sihc/models/sihc/sublayer_kernels.py:280-284).
+//
+// A thread owns (channel lane, slot s, quarter q of the events): EQ = ceil(E/4) events of ONE slot.  Per token it reads
+// its slot's carrier vector and its EQ gradient vectors from the block's shared tile (EQ + 1 reads for 2*EQ*V FMAs),
+// accumulates dalpha for its (events, slot) - unique in the block, so no block reduction - and forms the partial
+// sum_{l in quarter} alpha_l * g_l of dx for its slot; the four quarters of a (lane, slot) are four adjacent threads of a
+// warp, so the partial is completed by two shuffle steps (fixed order: deterministic) and stored by quarter 0.
+template <typename T, int EQ, int TK, int NST>
+__global__ void __launch_bounds__(256, 2) read_bwd_tiled_kernel(const __grid_constant__ WGradReadParams p) {
+    constexpr int S = 4;
+    constexpr int V = 16 / int(sizeof(T));
+    constexpr int ROWS = S + 4 * EQ;                       // tile rows per token: carrier slots, then (padded) events
+    constexpr uint32_t CL = kReadBwdTileLanes;             // channel vectors per block
+    constexpr uint32_t RS = kReadBwdTileRowStride;         // row stride in vectors: the four adjacent rows a warp reads
+                                                           // (its four quarters, or its four slots) fall in distinct banks
+    typedef VecIO<T, V> IO;
+    typedef typename IO::Raw Raw;
+    extern __shared__ __align__(16) unsigned char tile_bytes[];
+    const Tiling& t = p.t;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t q = tid & 3u, s = (tid >> 2) & 3u, lane = tid >> 4;
+    const uint32_t cv = blockIdx.y * CL + lane;
+    const bool active = cv < t.ncv;
+    const uint32_t c0 = cv * V;
+    Raw* tile = reinterpret_cast<Raw*>(tile_bytes);        // [NST][TK][ROWS][RS]; event l sits in row S + (l % EQ)*4 + l / EQ
+    constexpr uint32_t stage_vecs = TK * ROWS * RS;
+    const T* __restrict__ x = static_cast<const T*>(p.x);
+
+    // Copy plan: per token the tile has ROWS x CL vectors; a thread copies vector `tid` and vector `tid + 256` of them, so
+    // its rows, its lane and its source pointers are fixed for the whole launch.
+    const uint32_t ln = tid & (CL - 1);
+    const bool ln_ok = blockIdx.y * CL + ln < t.ncv;
+    const size_t coff = static_cast<size_t>(blockIdx.y * CL + ln) * V;
+    const T* src_row[2];
+    uint32_t dst_row[2];
+    bool is_x[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const uint32_t row = (tid >> 4) + 16u * k;         // 0..31; rows >= ROWS do not exist
+        is_x[k] = row < S;
+        src_row[k] = nullptr;
+        dst_row[k] = 0;
+        if (row < S) {
+            src_row[k] = x + slot_offset<S>(static_cast<int>(row), t.g, t.C) + coff;
+            dst_row[k] = row * RS + ln;
+        } else if (row < ROWS) {
+            const uint32_t l = row - S;
+            const T* gl = l < static_cast<uint32_t>(p.E) ? static_cast<const T*>(p.z.p[l]) : nullptr;
+            src_row[k] = gl ? gl + coff : nullptr;
+            dst_row[k] = (S + (l % EQ) * 4 + l / EQ) * RS + ln;
+            if (gl == nullptr) dst_row[k] |= 0x80000000u;  // a row to zero-fill
+        } else {
+            dst_row[k] = 0xffffffffu;                      // nothing to copy
+        }
+    }
+
+    auto issue = [&](uint32_t tl, int stage) {
+        const bool live = tl < t.ntiles;
+        Raw* sb = tile + static_cast<size_t>(stage) * stage_vecs;
+#pragma unroll
+        for (int tok = 0; tok < TK; ++tok) {
+            const uint32_t m = tl * TK + tok;
+            const bool ok = live && m < t.M && ln_ok;
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                if (dst_row[k] == 0xffffffffu) continue;
+                const bool fill = (dst_row[k] & 0x80000000u) != 0;
+                const T* src = x;
+                if (ok && !fill)
+                    src = is_x[k] ? src_row[k] + cell_origin<S>(m, t.g, t.C) : src_row[k] + static_cast<size_t>(m) * t.C;
+                cp_async<16>(sb + tok * (ROWS * RS) + (dst_row[k] & 0x7fffffffu), src, ok && !fill);
+            }
+        }
+        cp_async_commit();
+    };
+
+    float acc[EQ][V];
+    Raw ar[EQ];                                            // alpha[l][c0..c0+V)[s] of this thread's events, packed
+#pragma unroll
+    for (int j = 0; j < EQ; ++j) {
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[j][v] = 0.f;
+        const uint32_t l = q * EQ + j;
+        float f[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+            f[v] = (active && l < static_cast<uint32_t>(p.E))
+                       ? w_to_float<T>(__ldg(static_cast<const T*>(p.w) + (static_cast<size_t>(l) * t.C + c0 + v) * S + s)) : 0.f;
+        ar[j] = IO::pack(f);                               // exact: the values are storage values
+    }
+    T* __restrict__ dx = static_cast<T*>(p.out.p[0]);      // the carrier gradient travels in out.p[0]
+
+    uint32_t tl = blockIdx.x;
+#pragma unroll
+    for (int st = 0; st < NST - 1; ++st) issue(tl + st * gridDim.x, st);
+    int stage = 0;
+    for (; tl < t.ntiles; tl += gridDim.x) {
+        cp_async_wait<NST - 2>();
+        __syncthreads();
+        issue(tl + (NST - 1) * gridDim.x, stage == 0 ? NST - 1 : stage - 1);
+        const Raw* tb = tile + static_cast<size_t>(stage) * stage_vecs + lane;
+#pragma unroll
+        for (int tok = 0; tok < TK; ++tok) {
+            const Raw* tr = tb + tok * (ROWS * RS);
+            const Raw xr = tr[s * RS];
+            float part[V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) part[v] = 0.f;
+#pragma unroll
+            for (int j = 0; j < EQ; ++j) {
+                const Raw gr = tr[(S + j * 4 + q) * RS];
+                IO::fma_raw(xr, gr, acc[j]);
+                IO::fma_raw(ar[j], gr, part);
+            }
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                part[v] += __shfl_xor_sync(0xffffffffu, part[v], 1);
+                part[v] += __shfl_xor_sync(0xffffffffu, part[v], 2);
+            }
+            const uint32_t m = tl * TK + tok;
+            if (q == 0 && active && m < t.M)
+                IO::store(dx + cell_origin<S>(m, t.g, t.C) + slot_offset<S>(static_cast<int>(s), t.g, t.C) + c0, part);
+        }
+        stage = stage + 1 == NST ? 0 : stage + 1;
+    }
+    cp_async_wait<0>();
+    if (!active || p.partial == nullptr) return;
+    const uint32_t rows_total = static_cast<uint32_t>(p.E) * S;
+    float* dst = p.partial + static_cast<size_t>(blockIdx.x) * rows_total * t.C + c0;
+#pragma unroll
+    for (int j = 0; j < EQ; ++j) {
+        const uint32_t l = q * EQ + j;
+        if (l >= static_cast<uint32_t>(p.E)) break;
+        float* d = dst + (static_cast<size_t>(l) * S + s) * t.C;
+#pragma unroll
+        for (int v = 0; v < V; ++v) d[v] = acc[j][v];
+    }
+}
+
 // Shape of the tile ring: (tokens per stage, stages).  What matters is how many tokens of copies a block keeps in
 // flight, (stages - 1) x tokens: 8 is the optimum and 16 collapses (the threads stall issuing copies into a full
 // memory queue instead of computing).  Measured on B200, bf16, 4 slots, 65 536 tokens, width 768, GB/s:
@@ -122,11 +308,9 @@ template <typename F> cudaError_t dispatch_tile_shape(uint32_t groups, F&& f) {
     return f(std::integral_constant<int, kWGradTileTokens>{}, std::integral_constant<int, kWGradTileStages>{});
 }
 
-cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const void* const* z, float* partial,
-                               uint32_t* blocks) {
-    WGradParams p{};
-    p.x = carrier; p.partial = partial; p.E = pb.E;
-    for (int l = 0; l < pb.E; ++l) p.z.p[l] = z[l];
+namespace {
+template <bool READ, typename P>
+cudaError_t launch_tiled(const Problem& pb, P& p, uint32_t* blocks) {
     return dispatch_types(pb.dtype, pb.dtype, [&](auto tt_, auto) {
         using T = decltype(tt_);
         return dispatch_slots(pb.S, [&](auto s_) {
@@ -137,7 +321,7 @@ cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const voi
             else return dispatch_tile_shape(static_cast<uint32_t>((pb.E + EC - 1) / EC), [&](auto tk_, auto nst_) {
                 constexpr int TK = decltype(tk_)::value;
                 constexpr int NST = decltype(nst_)::value;
-                auto kernel = wgrad_tiled_kernel<T, S, V, TK, NST>;
+                auto kernel = wgrad_tiled_kernel<T, S, V, TK, NST, READ, P>;
                 const uint32_t ncv = pb.C / V;
                 const uint32_t groups = static_cast<uint32_t>((pb.E + EC - 1) / EC);
                 // channel lanes: what the block's threads and 200 KB of shared memory leave per event group, split evenly
@@ -149,7 +333,8 @@ cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const voi
                 const size_t vb = static_cast<size_t>(V) * sizeof(T);
                 const size_t per_lane = NST * TK * vb * (static_cast<size_t>(S) + static_cast<size_t>(EC) * groups);
                 uint32_t block_threads = kWGradTileDefaultThreads;
-                if (tuning().threads > 0) block_threads = static_cast<uint32_t>(tuning().threads < kWGradTileThreads ? tuning().threads : kWGradTileThreads);
+                const uint32_t limit = READ ? kWGradTileDefaultThreads : kWGradTileThreads;
+                if (tuning().threads > 0) block_threads = static_cast<uint32_t>(tuning().threads) < limit ? static_cast<uint32_t>(tuning().threads) : limit;
                 if (block_threads < groups) block_threads = groups;
                 uint32_t max_cl = block_threads / groups;
                 if (max_cl > kMaxDynamic / per_lane) max_cl = static_cast<uint32_t>(kMaxDynamic / per_lane);
@@ -157,6 +342,7 @@ cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const voi
                 const uint32_t gy = (ncv + max_cl - 1) / max_cl;
                 const uint32_t cl = (ncv + gy - 1) / gy;
                 const uint32_t threads = cl * groups;
+                if (threads > limit) return cudaErrorInvalidConfiguration;
                 const size_t smem = per_lane * cl;
                 if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kMaxDynamic)) return e;
                 Tiling& t = p.t;
@@ -177,6 +363,70 @@ cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const voi
                 return cudaGetLastError();
             });
         });
+    });
+}
+}  // namespace
+
+cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const void* const* z, float* partial,
+                               uint32_t* blocks) {
+    WGradParams p{};
+    p.x = carrier; p.partial = partial; p.E = pb.E;
+    for (int l = 0; l < pb.E; ++l) p.z.p[l] = z[l];
+    return launch_tiled<false>(pb, p, blocks);
+}
+
+bool wgrad_tiled_read_applies(const Problem& pb) {
+    return pb.V > 1 && pb.S == 4 && pb.E >= 16 && pb.dtype == pb.wdtype && tuning().wgrad_tiled != 0;
+}
+
+cudaError_t launch_wgrad_tiled_read(const Problem& pb, const void* carrier, const void* const* z, const void* beta,
+                                    void* const* ddz, float* partial, uint32_t* blocks) {
+    WGradReadParams p{};
+    p.x = carrier; p.partial = partial; p.E = pb.E; p.w = beta;
+    for (int l = 0; l < pb.E; ++l) { p.z.p[l] = z[l]; p.out.p[l] = ddz[l]; }
+    return launch_tiled<true>(pb, p, blocks);
+}
+
+bool read_bwd_tiled_applies(const Problem& pb) {
+    return pb.V > 1 && pb.S == 4 && pb.E >= 16 && pb.dtype == pb.wdtype && tuning().wgrad_tiled != 0 && tuning().stage_smem != 0;
+}
+
+cudaError_t launch_read_bwd_tiled(const Problem& pb, const void* carrier, const void* const* g, const void* alpha, void* dx,
+                                  float* partial, uint32_t* blocks) {
+    WGradReadParams p{};
+    p.x = carrier; p.partial = partial; p.E = pb.E; p.w = alpha; p.out.p[0] = dx;
+    for (int l = 0; l < pb.E; ++l) p.z.p[l] = g[l];
+    return dispatch_types(pb.dtype, pb.dtype, [&](auto tt_, auto) {
+        using T = decltype(tt_);
+        constexpr int V = 16 / int(sizeof(T));
+        constexpr int TK = 4, NST = 3;
+        auto go = [&](auto eq_) {
+            constexpr int EQ = decltype(eq_)::value;
+            auto kernel = read_bwd_tiled_kernel<T, EQ, TK, NST>;
+            const uint32_t ncv = pb.C / V, cl = kReadBwdTileLanes;
+            const uint32_t gy = (ncv + cl - 1) / cl;
+            const size_t smem = static_cast<size_t>(NST) * TK * (4 + 4 * EQ) * kReadBwdTileRowStride * 16;
+            if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), 200 * 1024)) return e;
+            Tiling& t = p.t;
+            t.M = pb.M; t.g = pb.g; t.C = pb.C; t.ncv = ncv; t.cl = cl; t.tl = 16;
+            t.ntiles = (pb.M + TK - 1) / TK;
+            int nb = cached_occupancy(reinterpret_cast<const void*>(kernel), 256, smem);
+            const int cap = tuning().rbps > 0 ? tuning().rbps : 2;
+            if (nb > cap) nb = cap;
+            if (nb < 1) nb = 1;
+            uint32_t gx = static_cast<uint32_t>(sm_count()) * static_cast<uint32_t>(nb) / gy;
+            const uint32_t bound = partial_blocks_bound(pb.M);
+            if (gx > bound) gx = bound;
+            if (gx < 1) gx = 1;
+            if (gx > t.ntiles) gx = t.ntiles;
+            if (blocks) *blocks = gx;
+            kernel<<<dim3(gx, gy, 1), 256, smem, pb.stream>>>(p);
+            count_launch();
+            return cudaGetLastError();
+        };
+        if (pb.E <= 16) return go(std::integral_constant<int, 4>{});
+        if (pb.E <= 20) return go(std::integral_constant<int, 5>{});
+        return go(std::integral_constant<int, 6>{});
     });
 }
 

@@ -432,6 +432,51 @@ def test_stage_weight_gradient_tiled_and_per_thread_forms(R, tiled, slots, b, g,
             close(da_holes[i], oda[i].to(dtype), dtype, f"dalpha[{i}] with unused outputs")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("b,g,c,events", [(3, 7, 768, 24), (2, 5, 1152, 16), (2, 6, 72, 20), (1, 16, 776, 18), (5, 3, 8, 24)])
+def test_stage_adjoints_in_one_pass_and_as_two_kernels(R, b, g, c, events, dtype):
+    """With four slots and 16 or more events both adjoints of the stage read (dx, dalpha) and of the stage write (ddz, dbeta)
+    come from one pass over the carrier and the event tensors; `"stage_smem" = 0` restores the two-kernel forms.  Both
+    must match the fp64 oracle; the write side is the same arithmetic in the same order, hence bit-identical; a read
+    output nobody used (no gradient) contributes nothing to dx and leaves its dalpha rows exactly zero in both."""
+    from residual_stream_burden_b200 import _lib
+    torch.manual_seed(4100 + events + c)
+    slots = 4
+    x = torch.randn(b, g * 2, g * 2, c).to(dtype)
+    w = (0.25 + 0.05 * torch.randn(events, c, slots)).to(dtype)
+    ev = [torch.randn(b, g * g, c).to(dtype) for _ in range(events)]
+    holes = [t if i % 5 != 2 else None for i, t in enumerate(ev)]
+    xd, wd = x.to(DEV), w.to(DEV)
+    evd = [t.to(DEV) for t in ev]
+    holesd = [t.to(DEV) if t is not None else None for t in holes]
+    got = {}
+    for form, knob in (("one pass", -1), ("two kernels", 0)):
+        _lib.tune("stage_smem", knob)
+        try:
+            n0 = _lib.lib.sihc_launch_count()
+            dx, da = R.ops._read_backward_op(xd, holesd, wd, True, True)
+            n1 = _lib.lib.sihc_launch_count()
+            ddz, db = R.ops._write_backward_op(xd, evd, wd, True, True)
+            n2 = _lib.lib.sihc_launch_count()
+            torch.cuda.synchronize()
+        finally:
+            _lib.tune("stage_smem", -1)
+        got[form] = (dx, da, torch.stack(ddz), db)
+        assert (n1 - n0, n2 - n1) == ((2, 2) if form == "one pass" else (3, 3)), (form, n1 - n0, n2 - n1)
+    odx, oda = O.read_backward(x, holes, w, acc=torch.float64)
+    oddz, odb = O.write_backward(x, ev, w, acc=torch.float64)
+    for form, (dx, da, ddz, db) in got.items():
+        close(dx, odx, dtype, f"dx ({form})")
+        close(da, oda.to(dtype), dtype, f"dalpha ({form})")
+        close(ddz, torch.stack(oddz), dtype, f"ddz ({form})")
+        close(db, odb.to(dtype), dtype, f"dbeta ({form})")
+        for i, t in enumerate(holes):
+            if t is None:
+                assert not da[i].any(), (form, i)
+    assert torch.equal(got["one pass"][2], got["two kernels"][2])
+    assert torch.equal(got["one pass"][3], got["two kernels"][3])
+
+
 @pytest.mark.parametrize("active,c,dtype,gamma_fp32", [(3, 64, torch.bfloat16, False), (5, 768, torch.bfloat16, True),
                                                        (8, 128, torch.float32, True), (12, 1152, torch.bfloat16, False),
                                                        (23, 768, torch.bfloat16, False), (23, 64, torch.bfloat16, True)])

@@ -212,6 +212,7 @@ int sihc_tune(const char* name, int value) {
     else if (!std::strcmp(name, "tri_chunk")) t.tri_chunk = value;
     else if (!std::strcmp(name, "wgrad_tiled")) t.wgrad_tiled = tri;    // 1 block-tiled, 0 per-thread weight gradient
     else if (!std::strcmp(name, "half_vectors")) t.half_vectors = tri;
+    else if (!std::strcmp(name, "one_pass_adjoints")) t.one_pass_adjoints = tri;
     else if (!std::strcmp(name, "token_lanes")) t.token_lanes = value;
     else if (!std::strcmp(name, "stage_smem")) t.stage_smem = tri;
     else if (!std::strcmp(name, "stage_smem_default")) t.stage_smem = -1;
@@ -339,7 +340,7 @@ int sihc_read_bwd(const void* x, const void* const* g, const void* alpha, void* 
     } else if (events == 1) {
         e = launch_read_bwd1(pb, x, g[0], alpha, dx, partial, &blocks);
     } else if (dx && dalpha && read_bwd_tiled_applies(pb)) {
-        // both adjoints from one pass over x and the gradients: 2S + E elements ("stage_smem" = 0 restores two kernels)
+        // both adjoints from one pass over x and the gradients: 2S + E elements ("one_pass_adjoints" = 0 restores two kernels)
         e = launch_read_bwd_tiled(pb, x, g, alpha, dx, partial, &blocks);
     } else {
         e = cudaSuccess;
@@ -382,8 +383,8 @@ int sihc_write_bwd(const void* h, const void* const* dz, const void* beta, void*
                                    kWriteBwdRingThreads);
     } else if (events == 1) {
         e = launch_write_bwd1(pb, h, dbeta ? dz[0] : nullptr, beta, want_ddz ? ddz[0] : nullptr, partial, &blocks);
-    } else if (want_ddz && dbeta && wgrad_tiled_read_applies(pb) && tuning().stage_smem != 0) {
-        // both adjoints from one pass over h: S + 2E elements (the "stage_smem" = 0 knob restores the two-kernel form)
+    } else if (want_ddz && dbeta && wgrad_tiled_read_applies(pb) && tuning().one_pass_adjoints != 0) {
+        // both adjoints from one pass over h: S + 2E elements ("one_pass_adjoints" = 0 restores the two-kernel form)
         e = launch_wgrad_tiled_read(pb, h, dz, beta, ddz, partial, &blocks);
     } else {
         e = cudaSuccess;

@@ -388,7 +388,7 @@ cudaError_t launch_wgrad_tiled_read(const Problem& pb, const void* carrier, cons
 }
 
 bool read_bwd_tiled_applies(const Problem& pb) {
-    return pb.V > 1 && pb.S == 4 && pb.E >= 16 && pb.dtype == pb.wdtype && tuning().wgrad_tiled != 0 && tuning().stage_smem != 0;
+    return pb.V > 1 && pb.S == 4 && pb.E >= 16 && pb.dtype == pb.wdtype && tuning().wgrad_tiled != 0 && tuning().one_pass_adjoints != 0;
 }
 
 cudaError_t launch_read_bwd_tiled(const Problem& pb, const void* carrier, const void* const* g, const void* alpha, void* dx,

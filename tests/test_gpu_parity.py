@@ -436,7 +436,7 @@ def test_stage_weight_gradient_tiled_and_per_thread_forms(R, tiled, slots, b, g,
 @pytest.mark.parametrize("b,g,c,events", [(3, 7, 768, 24), (2, 5, 1152, 16), (2, 6, 72, 20), (1, 16, 776, 18), (5, 3, 8, 24)])
 def test_stage_adjoints_in_one_pass_and_as_two_kernels(R, b, g, c, events, dtype):
     """With four slots and 16 or more events both adjoints of the stage read (dx, dalpha) and of the stage write (ddz, dbeta)
-    come from one pass over the carrier and the event tensors; `"stage_smem" = 0` restores the two-kernel forms.  Both
+    come from one pass over the carrier and the event tensors; `"one_pass_adjoints" = 0` restores the two-kernel forms.  Both
     must match the fp64 oracle; the write side is the same arithmetic in the same order, hence bit-identical; a read
     output nobody used (no gradient) contributes nothing to dx and leaves its dalpha rows exactly zero in both."""
     from residual_stream_burden_b200 import _lib
@@ -451,7 +451,7 @@ def test_stage_adjoints_in_one_pass_and_as_two_kernels(R, b, g, c, events, dtype
     holesd = [t.to(DEV) if t is not None else None for t in holes]
     got = {}
     for form, knob in (("one pass", -1), ("two kernels", 0)):
-        _lib.tune("stage_smem", knob)
+        _lib.tune("one_pass_adjoints", knob)
         try:
             n0 = _lib.lib.sihc_launch_count()
             dx, da = R.ops._read_backward_op(xd, holesd, wd, True, True)
@@ -460,7 +460,7 @@ def test_stage_adjoints_in_one_pass_and_as_two_kernels(R, b, g, c, events, dtype
             n2 = _lib.lib.sihc_launch_count()
             torch.cuda.synchronize()
         finally:
-            _lib.tune("stage_smem", -1)
+            _lib.tune("one_pass_adjoints", -1)
         got[form] = (dx, da, torch.stack(ddz), db)
         assert (n1 - n0, n2 - n1) == ((2, 2) if form == "one pass" else (3, 3)), (form, n1 - n0, n2 - n1)
     odx, oda = O.read_backward(x, holes, w, acc=torch.float64)

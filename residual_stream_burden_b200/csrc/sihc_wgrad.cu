@@ -161,7 +161,8 @@ constexpr uint32_t kReadBwdTileRowStride = 18;
 // its slot's carrier vector and its EQ gradient vectors from the block's shared tile (EQ + 1 reads for 2*EQ*V FMAs),
 // accumulates dalpha for its (events, slot) - unique in the block, so no block reduction - and forms the partial
 // sum_{l in quarter} alpha_l * g_l of dx for its slot; the four quarters of a (lane, slot) are four adjacent threads of a
-// warp, so the partial is completed by two shuffle steps (fixed order: deterministic) and stored by quarter 0.
+// warp, so the partial is completed by a two-step reduce-scatter of shuffles (fixed order: deterministic), after which
+// each of the four stores its V/4 channels.
 template <typename T, int EQ, int TK, int NST>
 __global__ void __launch_bounds__(256, 2) read_bwd_tiled_kernel(const __grid_constant__ WGradReadParams p) {
     constexpr int S = 4;
@@ -211,9 +212,11 @@ __global__ void __launch_bounds__(256, 2) read_bwd_tiled_kernel(const __grid_con
         }
     }
 
+    __shared__ size_t origin[NST][TK];                     // carrier offset of each token's cell, for the dx stores
     auto issue = [&](uint32_t tl, int stage) {
         const bool live = tl < t.ntiles;
         Raw* sb = tile + static_cast<size_t>(stage) * stage_vecs;
+        if (tid < TK) origin[stage][tid] = cell_origin<S>(tl * TK + tid, t.g, t.C);
 #pragma unroll
         for (int tok = 0; tok < TK; ++tok) {
             const uint32_t m = tl * TK + tok;
@@ -245,7 +248,9 @@ __global__ void __launch_bounds__(256, 2) read_bwd_tiled_kernel(const __grid_con
                        ? w_to_float<T>(__ldg(static_cast<const T*>(p.w) + (static_cast<size_t>(l) * t.C + c0 + v) * S + s)) : 0.f;
         ar[j] = IO::pack(f);                               // exact: the values are storage values
     }
-    T* __restrict__ dx = static_cast<T*>(p.out.p[0]);      // the carrier gradient travels in out.p[0]
+    // the carrier gradient travels in out.p[0]; this thread's V/4 channels of its slot, relative to a cell origin
+    T* __restrict__ dx_slot = static_cast<T*>(p.out.p[0]) + slot_offset<S>(static_cast<int>(s), t.g, t.C) + c0 +
+                              (q & 1u) * (V / 2) + (q >> 1) * (V / 4);
 
     uint32_t tl = blockIdx.x;
 #pragma unroll
@@ -269,14 +274,24 @@ __global__ void __launch_bounds__(256, 2) read_bwd_tiled_kernel(const __grid_con
                 IO::fma_raw(xr, gr, acc[j]);
                 IO::fma_raw(ar[j], gr, part);
             }
+            // reduce-scatter over the four quarters: (q0 + q1) + (q2 + q3) for every channel, each thread ending up with
+            // V/4 of the V sums
+            float half[V / 2], mine[V / 4];
 #pragma unroll
-            for (int v = 0; v < V; ++v) {
-                part[v] += __shfl_xor_sync(0xffffffffu, part[v], 1);
-                part[v] += __shfl_xor_sync(0xffffffffu, part[v], 2);
+            for (int k = 0; k < V / 2; ++k) {
+                const float send = (q & 1u) ? part[k] : part[k + V / 2];
+                const float keep = (q & 1u) ? part[k + V / 2] : part[k];
+                half[k] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+            }
+#pragma unroll
+            for (int k = 0; k < V / 4; ++k) {
+                const float send = (q & 2u) ? half[k] : half[k + V / 4];
+                const float keep = (q & 2u) ? half[k + V / 4] : half[k];
+                mine[k] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
             }
             const uint32_t m = tl * TK + tok;
-            if (q == 0 && active && m < t.M)
-                IO::store(dx + cell_origin<S>(m, t.g, t.C) + slot_offset<S>(static_cast<int>(s), t.g, t.C) + c0, part);
+            if (active && m < t.M)
+                VecIO<T, V / 4>::store(dx_slot + origin[stage][tok], mine);
         }
         stage = stage + 1 == NST ? 0 : stage + 1;
     }

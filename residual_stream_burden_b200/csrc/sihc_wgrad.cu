@@ -439,6 +439,7 @@ cudaError_t launch_read_bwd_tiled(const Problem& pb, const void* carrier, const 
             count_launch();
             return cudaGetLastError();
         };
+        static_assert(kMaxEvents <= 24, "the widest instantiation covers 4 x 6 events");
         if (pb.E <= 16) return go(std::integral_constant<int, 4>{});
         if (pb.E <= 20) return go(std::integral_constant<int, 5>{});
         return go(std::integral_constant<int, 6>{});

@@ -22,7 +22,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
-DEFAULT_SOURCE = os.environ.get("SIHC_REFERENCE_ROOT", "/root/reference")      # the read-only reference checkout
+# the read-only reference checkout: $SIHC_REFERENCE_ROOT, else a folder named `reference` in the home directory
+DEFAULT_SOURCE = os.environ.get("SIHC_REFERENCE_ROOT", os.path.join(os.path.expanduser("~"), "reference"))
 
 
 def make_ref(source: str = DEFAULT_SOURCE) -> str | None:

@@ -249,6 +249,7 @@ int sihc_tri_dgamma(const void* const* g, const void* const* dz, float* dgamma, 
  *   "stage_smem" (0 = stage coefficients from L1, 1 = from shared memory),
  *   "wgrad_tiled" (0 = per-thread, 1 = block-tiled stage weight gradient),
  *   "one_pass_adjoints" (0 = stage read/write backward always as two kernels),
+ *   "one_pass_min_events" (fewest events for which they run as one pass; <= 0 restores the default),
  *   "half_vectors" (fused literal adjoint: 1 = half-width vectors and twice the channel lanes): a negative
  *   value restores the per-kernel default ("ring_default" / "stage_smem_default"
  *   with any value do the same).

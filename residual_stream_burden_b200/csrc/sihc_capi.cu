@@ -213,6 +213,7 @@ int sihc_tune(const char* name, int value) {
     else if (!std::strcmp(name, "wgrad_tiled")) t.wgrad_tiled = tri;    // 1 block-tiled, 0 per-thread weight gradient
     else if (!std::strcmp(name, "half_vectors")) t.half_vectors = tri;
     else if (!std::strcmp(name, "one_pass_adjoints")) t.one_pass_adjoints = tri;
+    else if (!std::strcmp(name, "one_pass_min_events")) t.one_pass_min_events = value;
     else if (!std::strcmp(name, "token_lanes")) t.token_lanes = value;
     else if (!std::strcmp(name, "stage_smem")) t.stage_smem = tri;
     else if (!std::strcmp(name, "stage_smem_default")) t.stage_smem = -1;

@@ -25,6 +25,7 @@ struct Tuning {
     int wgrad_tiled = -1;       // stage weight gradient: 1 block-tiled kernel, 0 per-thread kernel (-1: default)
     int token_lanes = 0;        // fused literal adjoint: fewest token lanes per block (0: default 4 or 6)
     int one_pass_adjoints = -1; // stage read/write backward: 0 two kernels, otherwise one pass where it applies
+    int one_pass_min_events = 0; // fewest events for the one-pass forms; <= 0: kOnePassMinEvents
     int half_vectors = -1;      // fused literal adjoint: 1 half-width vectors and twice the threads, 0 full width, -1 default
     int stage_smem = -1;        // stage read/write coefficients: 1 staged in shared memory, 0 re-read from L1,
                                 // -1 default (staged whenever the vector path applies)

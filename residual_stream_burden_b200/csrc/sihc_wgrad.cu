@@ -390,8 +390,11 @@ cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const voi
     return launch_tiled<false>(pb, p, blocks);
 }
 
+constexpr int kOnePassMinEvents = 16;
+static int one_pass_min_events() { return tuning().one_pass_min_events > 0 ? tuning().one_pass_min_events : kOnePassMinEvents; }
+
 bool wgrad_tiled_read_applies(const Problem& pb) {
-    return pb.V > 1 && pb.S == 4 && pb.E >= 16 && pb.dtype == pb.wdtype && tuning().wgrad_tiled != 0;
+    return pb.V > 1 && pb.S == 4 && pb.E >= one_pass_min_events() && pb.E >= 2 && pb.dtype == pb.wdtype && tuning().wgrad_tiled != 0;
 }
 
 cudaError_t launch_wgrad_tiled_read(const Problem& pb, const void* carrier, const void* const* z, const void* beta,
@@ -403,7 +406,8 @@ cudaError_t launch_wgrad_tiled_read(const Problem& pb, const void* carrier, cons
 }
 
 bool read_bwd_tiled_applies(const Problem& pb) {
-    return pb.V > 1 && pb.S == 4 && pb.E >= 16 && pb.dtype == pb.wdtype && tuning().wgrad_tiled != 0 && tuning().one_pass_adjoints != 0;
+    return pb.V > 1 && pb.S == 4 && pb.E >= one_pass_min_events() && pb.E >= 2 && pb.dtype == pb.wdtype && tuning().wgrad_tiled != 0 &&
+           tuning().one_pass_adjoints != 0;
 }
 
 cudaError_t launch_read_bwd_tiled(const Problem& pb, const void* carrier, const void* const* g, const void* alpha, void* dx,
@@ -440,6 +444,9 @@ cudaError_t launch_read_bwd_tiled(const Problem& pb, const void* carrier, const 
             return cudaGetLastError();
         };
         static_assert(kMaxEvents <= 24, "the widest instantiation covers 4 x 6 events");
+        if (pb.E <= 4) return go(std::integral_constant<int, 1>{});
+        if (pb.E <= 8) return go(std::integral_constant<int, 2>{});
+        if (pb.E <= 12) return go(std::integral_constant<int, 3>{});
         if (pb.E <= 16) return go(std::integral_constant<int, 4>{});
         if (pb.E <= 20) return go(std::integral_constant<int, 5>{});
         return go(std::integral_constant<int, 6>{});

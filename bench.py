@@ -427,7 +427,7 @@ def run_stage_ops(args, device, steps, warmup):
     256 tokens, n=4, width 768, E=24 events): read(E), triangular(E-1), write(E) and their backward calls, plus the
     literal schedule's fused step and its fused adjoint, the one-pass stage coefficient gradient and the device's
     write-only bandwidth.  GB/s are algorithmic bytes (read S+E, write 2S+E, triangular J+2, read bwd 2S+E and
-    write bwd S+2E where one pass produces both adjoints (4 slots, >= 16 events) else 2(S+E) as two kernels, triangular bwd
+    write bwd S+2E where one pass produces both adjoints (4 slots; >= 12 and >= 8 events) else 2(S+E) as two kernels, triangular bwd
     2J+1, literal step 2S+2, its adjoint 3S+3, stage dgamma 2(E-1)) over the CUDA-event time of the C ABI call; `value` is the six factored-stage operators as a set.  The reference's own
     Triton operators are timed on the same tensors as a labelled comparator."""
     from residual_stream_burden_b200 import _lib
@@ -464,13 +464,13 @@ def run_stage_ops(args, device, steps, warmup):
         "read_fwd": (lambda: lib.sihc_read_fwd(x.data_ptr(), w.data_ptr(), p_out, E, *geom), S + E),
         "triangular_fwd": (lambda: lib.sihc_tri_fwd(out[0].data_ptr(), p_dz, gam.data_ptr(), y.data_ptr(), J, tokens, C, code, code, st), J + 2),
         "write_fwd": (lambda: lib.sihc_write_fwd(x.data_ptr(), p_dz, w.data_ptr(), y.data_ptr(), E, *geom), 2 * S + E),
-        # one pass (S+2E, 2S+E) where the weight-gradient kernel also produces the other adjoint (4 slots, >= 16 events),
-        # else two kernels
+        # one pass (S+2E, 2S+E) where the weight-gradient kernel also produces the other adjoint (4 slots; write from 8
+        # events, read from 12), else two kernels
         "write_bwd": (lambda: lib.sihc_write_bwd(gy.data_ptr(), p_dz, w.data_ptr(), p_out, dw.data_ptr(), ws.data_ptr(), ws.numel(), E, *geom),
-                      S + 2 * E if (S == 4 and E >= 16) else 2 * (S + E)),
+                      S + 2 * E if (S == 4 and E >= 8) else 2 * (S + E)),
         "triangular_bwd": (lambda: lib.sihc_tri_bwd(out[0].data_ptr(), p_dz, gam.data_ptr(), p_out, dgam.data_ptr(), ws.data_ptr(), ws.numel(), J, tokens, C, code, code, st), 2 * J + 1),
         "read_bwd": (lambda: lib.sihc_read_bwd(x.data_ptr(), p_dz, w.data_ptr(), y.data_ptr(), dw.data_ptr(), ws.data_ptr(), ws.numel(), E, *geom),
-                     2 * S + E if (S == 4 and E >= 16) else 2 * (S + E)),
+                     2 * S + E if (S == 4 and E >= 12) else 2 * (S + E)),
     }
     # literal schedule: one event's write fused with the next read (2S+2) and the fused adjoint of that step (3S+3)
     dw2 = torch.empty(2, C, S, device=device, dtype=torch.float32)

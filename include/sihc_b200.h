@@ -140,7 +140,7 @@ size_t sihc_wgrad_workspace_bytes(int events, int64_t batch, int grid, int kh, i
  * materialises zeros, :283).  `dx` or `dalpha` may be NULL to skip that output.
  * The reduction over tokens is deterministic (no atomics): fixed per-block
  * partials in `workspace`, then a fixed-order finishing pass.
- * With 4 slots, 16 or more events, weights in the tensor dtype and both outputs wanted,
+ * With 4 slots, 12 or more events, weights in the tensor dtype and both outputs wanted,
  * one kernel produces dx and the dalpha partials from a single pass over x and the
  * gradients (2*slots + events elements per token and channel; the two-kernel form, and
  * the reference, read the gradients twice).  dx is then summed per quarter of the events
@@ -187,9 +187,10 @@ int sihc_read_bwd_static(const void* x, const void* const* g, const void* alpha,
  * Replaces `_write_backward` (sihc/models/sihc/sublayer_kernels.py:300-303), i.e.
  * `sublayer_read(grad, beta)` plus `_weights_backward(grad, updates, beta)`.
  * `ddz` (the array) or `dbeta` may be NULL to skip that output.
- * With 4 slots, 16 or more events, weights in the tensor dtype and both outputs wanted,
+ * With 4 slots, 8 or more events, weights in the tensor dtype and both outputs wanted,
  * one kernel produces ddz and the dbeta partials from a single pass over h and the updates
- * (slots + 2*events elements per token and channel), bit-identical to the two-kernel form.
+ * (slots + 2*events elements per token and channel); ddz is bit-identical to the two-kernel
+ * form, and so is dbeta from 16 events up (below, the two-kernel form sums in another order).
  */
 int sihc_write_bwd(const void* h, const void* const* dz, const void* beta, void* const* ddz,
                    float* dbeta, void* workspace, size_t workspace_bytes, int events,
@@ -249,7 +250,8 @@ int sihc_tri_dgamma(const void* const* g, const void* const* dz, float* dgamma, 
  *   "stage_smem" (0 = stage coefficients from L1, 1 = from shared memory),
  *   "wgrad_tiled" (0 = per-thread, 1 = block-tiled stage weight gradient),
  *   "one_pass_adjoints" (0 = stage read/write backward always as two kernels),
- *   "one_pass_min_events" (fewest events for which they run as one pass; <= 0 restores the default),
+ *   "one_pass_min_events" (fewest events for which they run as one pass; <= 0 restores the defaults,
+ *   8 for the write backward and 12 for the read backward),
  *   "half_vectors" (fused literal adjoint: 1 = half-width vectors and twice the channel lanes): a negative
  *   value restores the per-kernel default ("ring_default" / "stage_smem_default"
  *   with any value do the same).

@@ -25,7 +25,7 @@ struct Tuning {
     int wgrad_tiled = -1;       // stage weight gradient: 1 block-tiled kernel, 0 per-thread kernel (-1: default)
     int token_lanes = 0;        // fused literal adjoint: fewest token lanes per block (0: default 4 or 6)
     int one_pass_adjoints = -1; // stage read/write backward: 0 two kernels, otherwise one pass where it applies
-    int one_pass_min_events = 0; // fewest events for the one-pass forms; <= 0: kOnePassMinEvents
+    int one_pass_min_events = 0; // fewest events for the one-pass forms; <= 0: 8 (write backward) and 12 (read backward)
     int half_vectors = -1;      // fused literal adjoint: 1 half-width vectors and twice the threads, 0 full width, -1 default
     int stage_smem = -1;        // stage read/write coefficients: 1 staged in shared memory, 0 re-read from L1,
                                 // -1 default (staged whenever the vector path applies)
@@ -104,7 +104,7 @@ cudaError_t launch_write_read_bwd(const Problem& pb, const void* h, const void* 
                                   const void* beta, const void* alpha_next, void* hh, void* ddz, float* partial,
                                   uint32_t* blocks);
 
-// One pass over the carrier and the E gradients for BOTH adjoints of the stage read (4 slots, 16..24 events, weights in
+// One pass over the carrier and the E gradients for BOTH adjoints of the stage read (4 slots, 12..24 events, weights in
 // the tensor dtype): dx = sum_l alpha_l * g_l and the dalpha partials: 2S + E elements instead of 2(S + E).
 bool read_bwd_tiled_applies(const Problem& pb);
 cudaError_t launch_read_bwd_tiled(const Problem& pb, const void* carrier, const void* const* g, const void* alpha, void* dx,

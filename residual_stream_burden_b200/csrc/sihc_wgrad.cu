@@ -390,11 +390,17 @@ cudaError_t launch_wgrad_tiled(const Problem& pb, const void* carrier, const voi
     return launch_tiled<false>(pb, p, blocks);
 }
 
-constexpr int kOnePassMinEvents = 16;
-static int one_pass_min_events() { return tuning().one_pass_min_events > 0 ? tuning().one_pass_min_events : kOnePassMinEvents; }
+// Fewest events at which one pass beats the two kernels (B200, bf16, 4 slots; ms one pass / two kernels):
+//   write backward  E=4: 0.386 / 0.285   E=6: 0.089 / 0.098 (8192 x 1152)   E=8: 0.389 / 0.473, 0.092 / 0.116   E=12: 0.517 / 0.679
+//   read backward   E=4: 0.457 / 0.294   E=8: 0.548 / 0.474, 0.116 / 0.115                     E=12: 0.576 / 0.674, 0.127 / 0.159
+// (65 536 tokens x 768 unless noted).  The "one_pass_min_events" knob overrides both.
+constexpr int kOnePassMinEventsWrite = 8;
+constexpr int kOnePassMinEventsRead = 12;
+static int one_pass_min_events(int builtin) { return tuning().one_pass_min_events > 0 ? tuning().one_pass_min_events : builtin; }
 
 bool wgrad_tiled_read_applies(const Problem& pb) {
-    return pb.V > 1 && pb.S == 4 && pb.E >= one_pass_min_events() && pb.E >= 2 && pb.dtype == pb.wdtype && tuning().wgrad_tiled != 0;
+    return pb.V > 1 && pb.S == 4 && pb.E >= one_pass_min_events(kOnePassMinEventsWrite) && pb.E >= 2 && pb.dtype == pb.wdtype &&
+           tuning().wgrad_tiled != 0;
 }
 
 cudaError_t launch_wgrad_tiled_read(const Problem& pb, const void* carrier, const void* const* z, const void* beta,
@@ -406,7 +412,7 @@ cudaError_t launch_wgrad_tiled_read(const Problem& pb, const void* carrier, cons
 }
 
 bool read_bwd_tiled_applies(const Problem& pb) {
-    return pb.V > 1 && pb.S == 4 && pb.E >= one_pass_min_events() && pb.E >= 2 && pb.dtype == pb.wdtype && tuning().wgrad_tiled != 0 &&
+    return pb.V > 1 && pb.S == 4 && pb.E >= one_pass_min_events(kOnePassMinEventsRead) && pb.E >= 2 && pb.dtype == pb.wdtype && tuning().wgrad_tiled != 0 &&
            tuning().one_pass_adjoints != 0;
 }
 

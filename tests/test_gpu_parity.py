@@ -433,10 +433,12 @@ def test_stage_weight_gradient_tiled_and_per_thread_forms(R, tiled, slots, b, g,
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("b,g,c,events", [(3, 7, 768, 24), (2, 5, 1152, 16), (2, 6, 72, 20), (1, 16, 776, 18), (5, 3, 8, 24)])
+@pytest.mark.parametrize("b,g,c,events", [(3, 7, 768, 24), (2, 5, 1152, 16), (2, 6, 72, 20), (1, 16, 776, 18), (5, 3, 8, 24),
+                                          (2, 6, 1152, 12), (3, 5, 768, 8), (2, 4, 64, 5), (2, 4, 72, 3)])
 def test_stage_adjoints_in_one_pass_and_as_two_kernels(R, b, g, c, events, dtype):
-    """With four slots and 16 or more events both adjoints of the stage read (dx, dalpha) and of the stage write (ddz, dbeta)
-    come from one pass over the carrier and the event tensors; `"one_pass_adjoints" = 0` restores the two-kernel forms.  Both
+    """With four slots and enough events (8 for the write, 12 for the read) both adjoints of the stage read (dx, dalpha) and of the stage write (ddz, dbeta)
+    come from one pass over the carrier and the event tensors (the `"one_pass_min_events"` knob lowers that event count: the
+    kernels themselves take any); `"one_pass_adjoints" = 0` restores the two-kernel forms.  Both
     must match the fp64 oracle; the write side is the same arithmetic in the same order, hence bit-identical; a read
     output nobody used (no gradient) contributes nothing to dx and leaves its dalpha rows exactly zero in both."""
     from residual_stream_burden_b200 import _lib
@@ -452,6 +454,7 @@ def test_stage_adjoints_in_one_pass_and_as_two_kernels(R, b, g, c, events, dtype
     got = {}
     for form, knob in (("one pass", -1), ("two kernels", 0)):
         _lib.tune("one_pass_adjoints", knob)
+        _lib.tune("one_pass_min_events", 2)
         try:
             n0 = _lib.lib.sihc_launch_count()
             dx, da = R.ops._read_backward_op(xd, holesd, wd, True, True)
@@ -461,8 +464,12 @@ def test_stage_adjoints_in_one_pass_and_as_two_kernels(R, b, g, c, events, dtype
             torch.cuda.synchronize()
         finally:
             _lib.tune("one_pass_adjoints", -1)
+            _lib.tune("one_pass_min_events", 0)
         got[form] = (dx, da, torch.stack(ddz), db)
-        assert (n1 - n0, n2 - n1) == ((2, 2) if form == "one pass" else (3, 3)), (form, n1 - n0, n2 - n1)
+        if form == "one pass":
+            assert (n1 - n0, n2 - n1) == (2, 2), (n1 - n0, n2 - n1)        # the pass and the finishing kernel
+        else:
+            assert n1 - n0 >= 3 and n2 - n1 >= 3, (n1 - n0, n2 - n1)
     odx, oda = O.read_backward(x, holes, w, acc=torch.float64)
     oddz, odb = O.write_backward(x, ev, w, acc=torch.float64)
     for form, (dx, da, ddz, db) in got.items():
@@ -474,7 +481,8 @@ def test_stage_adjoints_in_one_pass_and_as_two_kernels(R, b, g, c, events, dtype
             if t is None:
                 assert not da[i].any(), (form, i)
     assert torch.equal(got["one pass"][2], got["two kernels"][2])
-    assert torch.equal(got["one pass"][3], got["two kernels"][3])
+    if events >= 16:        # below, the two-kernel form takes the per-thread weight gradient: another summation order
+        assert torch.equal(got["one pass"][3], got["two kernels"][3])
 
 
 @pytest.mark.parametrize("active,c,dtype,gamma_fp32", [(3, 64, torch.bfloat16, False), (5, 768, torch.bfloat16, True),
